@@ -6,7 +6,8 @@ Paged specs are sorted into *groups* by what they keep (every position, or a win
 ``w``); each group has its own pool of page numbers and its own block table per request, and
 every layer of the group indexes its own tensor ``[pages, 2, kv_heads, page, head_dim]`` with
 the group's page numbers. Pages return to the group's pool when the request ends, or, in a
-window group, as soon as no later query can see them, and are handed out again (lowest number
+window group, as soon as no later query can see them (the pages of a group's kept first
+positions stay to the end), and are handed out again (lowest number
 first, so runs are reproducible). Page 0 of every pool and slot 0 are never handed out: padded
 rows of a batch point there. Fixed-size state (``SlotState``) is a row ``[*shape]`` per request
 in a ``[slots, *shape]`` tensor; a request starting at position 0 reads it as zeros by
@@ -74,6 +75,7 @@ class Group:
     window: int | None
     pages: FreeList
     members: list[StateKey] = field(default_factory=list)
+    keep_first: int = 0          # first positions of a sequence that a window never passes
 
 
 @dataclass
@@ -83,8 +85,9 @@ class RequestState:
     reserved: int = 0                                 # tokens pages are held for (>= length)
     tables: dict[tuple, list[int]] = field(default_factory=dict)  # group -> page per block (0: none)
     epoch: int = 0                                    # distinguishes two lives of one request id
-    # per group: blocks below this index have been given back (a window has passed them); every
-    # block from here to the end of the table holds a page
+    # per group: blocks below this index (and past the group's kept first positions) have been
+    # given back (a window has passed them); every block from here to the end of the table holds
+    # a page
     first_live: dict[tuple, int] = field(default_factory=dict)
     # tokens the tables of every group already reach (the shortest table times the page size):
     # an extension below this needs no page
@@ -121,9 +124,11 @@ class CacheManager:
             storage = getattr(spec, "storage", None)
             if storage == "paged":
                 g = self.groups.get(spec.group)
+                keep = int(getattr(spec, "keep_first", 0) or 0)
                 if g is None:
-                    g = self.groups[spec.group] = Group(spec.group, spec.window, FreeList(num_pages))
-                elif g.window != spec.window:
+                    g = self.groups[spec.group] = Group(spec.group, spec.window, FreeList(num_pages),
+                                                        keep_first=keep)
+                elif g.window != spec.window or g.keep_first != keep:
                     raise ValueError(f"state {key}: cache group {spec.group} holds a window of "
                                      f"{g.window}, this spec asks for {spec.window}")
                 g.members.append(key)
@@ -290,9 +295,11 @@ class CacheManager:
         for k, g in self._windowed:
             table = st.tables[k]
             passed = min(self._first_needed_block(g, st.length), len(table))
+            # the blocks of the kept first positions are never passed
+            start = max(st.first_live.get(k, 0), -(-g.keep_first // self.page_size))
             if self.poison:
-                self._poison_pages(g, [table[b] for b in range(st.first_live.get(k, 0), passed)])
-            for b in range(st.first_live.get(k, 0), passed):
+                self._poison_pages(g, [table[b] for b in range(start, passed)])
+            for b in range(start, passed):
                 g.pages.give(table[b])
                 table[b] = 0
             st.first_live[k] = max(st.first_live.get(k, 0), passed)

@@ -1,5 +1,6 @@
 """Typed configurations, one class per architecture, read from ``config.json``."""
 
+from tokenomos_b200.config.darizen import DarizenConfig
 from tokenomos_b200.config.lfm3 import ConfigError, Lfm3Config, RopeParams
 
-__all__ = ["ConfigError", "Lfm3Config", "RopeParams"]
+__all__ = ["ConfigError", "DarizenConfig", "Lfm3Config", "RopeParams"]

@@ -6,9 +6,14 @@
 // fallback of the 16-bit one.
 //
 // Score s = (q.k) * scale, key j visible to a query at position i iff j <= i and (no window or
-// i - j < window); online softmax; P rounded to the storage type before P.V; the row sum keeps
-// the unrounded values (Tokenomos kernels/attention/paged.py:67-76,150,267;
+// i - j < window or j < keep_first); online softmax; P rounded to the storage type before P.V
+// when `round_p` (the 16-bit reference's rounding), else kept in 32-bit; the row sum keeps the
+// unrounded values (Tokenomos kernels/attention/paged.py:67-76,150,267;
 // models/blocks/attention.py:31-40,173).
+// Options beyond the reference: `keep_first` (the first positions of a sequence stay visible
+// behind a window, at their true positions), `sink` (the softmax's denominator has one more
+// term, a key of score 0 without a value: p_j = exp(s_j) / (1 + sum exp(s_j))), values of
+// another size than the keys (Dv), cache rows wider than either (Dp).
 #include <math.h>
 
 #include "common.cuh"
@@ -26,15 +31,16 @@ attn_generic_kernel(const T* q, const T* kv_pool, T* out,
                     const int* positions, const int* tok_seq,
                     const int* block_table, int bt_stride,
                     const int* tile_tok0, const int* tile_ntok, int H,
-                    int Hkv, int D, int P, int window, float scale, int heads_per_chunk) {
+                    int Hkv, int D, int Dv, int Dp, int P, int window, int keep_first, int sink,
+                    int round_p, float scale, int heads_per_chunk) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ float smem[];
     const int DP = D + 1;
     float* Qs = smem;                 // [BM][D+1]
     float* Ks = Qs + BM * DP;         // [BN][D+1]
-    float* Vs = Ks + BN * DP;         // [BN][D]
-    float* Ss = Vs + BN * D;          // [BM][BN+1]
+    float* Vs = Ks + BN * DP;         // [BN][Dv]
+    float* Ss = Vs + BN * Dv;         // [BM][BN+1]
     __shared__ int row_pos[BM];
 
     const int G = H / Hkv;
@@ -70,29 +76,34 @@ attn_generic_kernel(const T* q, const T* kv_pool, T* out,
     const int r = tid >> 3;   // my row
     const int sub = tid & 7;  // my lane within the row
     const int my_pos = row_pos[r];
-    float m_i = -INFINITY, l_i = 0.f;
+    // a sink is a key of score 0 and no value that every row sees: the running maximum and sum
+    // start from it
+    float m_i = sink ? 0.f : -INFINITY, l_i = sink ? 1.f : 0.f;
     float acc[MAX_D / 8];
 #pragma unroll
     for (int k = 0; k < MAX_D / 8; ++k) acc[k] = 0.f;
 
-    for (int j0 = lo; j0 <= pos_last; j0 += BN) {
+    // the keys a tile reads: first the kept positions that lie before the window of the tile's
+    // first row, [0, keep_end), then everything from the window's start to the last row's position
+    const int keep_end = (keep_first > 0 && lo > 0) ? min(keep_first, lo) : 0;
+    const int n_keep = (keep_end + BN - 1) / BN;
+    const int n_main = (pos_last - lo) / BN + 1;
+    for (int it = 0; it < n_keep + n_main; ++it) {
+        const int j0 = it < n_keep ? it * BN : lo + (it - n_keep) * BN;
+        const int j_end = it < n_keep ? keep_end - 1 : pos_last;      // the last key of this range
         // load BN keys and values: 4 threads per key
         {
             const int kk = tid >> 2, part = tid & 3;
             const int j = j0 + kk;
-            if (j <= pos_last) {
+            if (j <= j_end) {
                 const int page = TK_PAGE(TK_K_ATTN_GENERIC, block_table[(size_t)seq * bt_stride + j / P]);
-                const size_t base = ((size_t)page * 2 * Hkv * P + (size_t)kvh * P + (j % P)) * D;
-                const size_t vbase = base + (size_t)Hkv * P * D;
-                for (int c = part; c < D; c += 4) {
-                    Ks[kk * DP + c] = to_f<T>(kv_pool[base + c]);
-                    Vs[kk * D + c] = to_f<T>(kv_pool[vbase + c]);
-                }
+                const size_t base = ((size_t)page * 2 * Hkv * P + (size_t)kvh * P + (j % P)) * Dp;
+                const size_t vbase = base + (size_t)Hkv * P * Dp;
+                for (int c = part; c < D; c += 4) Ks[kk * DP + c] = to_f<T>(kv_pool[base + c]);
+                for (int c = part; c < Dv; c += 4) Vs[kk * Dv + c] = to_f<T>(kv_pool[vbase + c]);
             } else {
-                for (int c = part; c < D; c += 4) {
-                    Ks[kk * DP + c] = 0.f;
-                    Vs[kk * D + c] = 0.f;
-                }
+                for (int c = part; c < D; c += 4) Ks[kk * DP + c] = 0.f;
+                for (int c = part; c < Dv; c += 4) Vs[kk * Dv + c] = 0.f;
             }
         }
         __syncthreads();
@@ -108,7 +119,8 @@ attn_generic_kernel(const T* q, const T* kv_pool, T* out,
             const float* kr = Ks + kk * DP;
             for (int c = 0; c < D; ++c) d += qr[c] * kr[c];
             d *= scale;
-            const bool visible = my_pos >= 0 && j <= my_pos && (window <= 0 || my_pos - j < window);
+            const bool visible = my_pos >= 0 && j <= j_end && j <= my_pos &&
+                                 (window <= 0 || my_pos - j < window || j < keep_first);
             s[jj] = visible ? d : -INFINITY;
             mx = fmaxf(mx, s[jj]);
         }
@@ -124,7 +136,7 @@ attn_generic_kernel(const T* q, const T* kv_pool, T* out,
         for (int jj = 0; jj < 4; ++jj) {
             const float p = expf(s[jj] - m_safe);
             psum += p;
-            Ss[r * (BN + 1) + sub + 8 * jj] = round_as<T>(p);
+            Ss[r * (BN + 1) + sub + 8 * jj] = round_p ? round_as<T>(p) : p;
         }
         psum += __shfl_xor_sync(0xffffffffu, psum, 1);
         psum += __shfl_xor_sync(0xffffffffu, psum, 2);
@@ -137,9 +149,9 @@ attn_generic_kernel(const T* q, const T* kv_pool, T* out,
 #pragma unroll
         for (int k = 0; k < MAX_D / 8; ++k) {
             const int c = sub + 8 * k;
-            if (c < D) {
+            if (c < Dv) {
                 float a = acc[k] * alpha;
-                for (int kk = 0; kk < BN; ++kk) a += pr[kk] * Vs[kk * D + c];
+                for (int kk = 0; kk < BN; ++kk) a += pr[kk] * Vs[kk * Dv + c];
                 acc[k] = a;
             }
         }
@@ -151,29 +163,33 @@ attn_generic_kernel(const T* q, const T* kv_pool, T* out,
 #pragma unroll
         for (int k = 0; k < MAX_D / 8; ++k) {
             const int c = sub + 8 * k;
-            if (c < D) out[((size_t)t * H + h) * D + c] = from_f<T>(acc[k] * inv);
+            if (c < Dv) out[((size_t)t * H + h) * Dv + c] = from_f<T>(acc[k] * inv);
         }
     }
 }
 
 // Shared memory the kernel needs for head size D (bytes).
-static size_t attn_generic_smem(int D) {
-    return ((size_t)BM * (D + 1) + (size_t)BN * (D + 1) + (size_t)BN * D + (size_t)BM * (BN + 1)) * sizeof(float);
+static size_t attn_generic_smem(int D, int Dv) {
+    return ((size_t)BM * (D + 1) + (size_t)BN * (D + 1) + (size_t)BN * Dv + (size_t)BM * (BN + 1)) * sizeof(float);
 }
 
 // Rows per tile this kernel takes: a tile holds `tokens_per_tile` tokens of one sequence with
 // `heads_per_chunk` query heads each, tokens_per_tile * heads_per_chunk <= 16.
 TK_API int tk_attn_generic_rows() { return BM; }
 
-// q, out: [T, H, D]; kv_pool: [pages, 2, Hkv, P, D]; tiles: first token and token count of each
-// tile (tokens of one sequence, consecutive positions); window <= 0: none.
+// q: [T, H, D]; out: [T, H, Dv]; kv_pool: [pages, 2, Hkv, P, Dp]; tiles: first token and token
+// count of each tile (tokens of one sequence, consecutive positions); window <= 0: none.
 TK_API int tk_attn_generic(const void* q, const void* kv_pool, void* out, const int* positions,
                            const int* tok_seq, const int* block_table, int bt_stride,
                            const int* tile_tok0, const int* tile_ntok, int n_tiles,
-                           int tokens_per_tile, int H, int Hkv, int D, int P, int window,
-                           float scale, int dtype, cudaStream_t stream) {
+                           int tokens_per_tile, int H, int Hkv, int D, int Dv, int Dp, int P, int window,
+                           int keep_first, int sink, int round_p, float scale, int dtype,
+                           cudaStream_t stream) {
     TK_CHECK_ARG(H > 0 && Hkv > 0 && H % Hkv == 0, "attention: %d query heads over %d KV heads", H, Hkv);
     TK_CHECK_ARG(D > 0 && D <= MAX_D, "attention: head_dim %d outside 1..%d", D, MAX_D);
+    TK_CHECK_ARG(Dv > 0 && Dv <= MAX_D, "attention: value size %d outside 1..%d", Dv, MAX_D);
+    TK_CHECK_ARG(Dp >= D && Dp >= Dv, "attention: cache rows of %d for heads of %d and %d", Dp, D, Dv);
+    TK_CHECK_ARG(keep_first >= 0, "attention: %d kept first positions", keep_first);
     TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attention: bad page size or tile count");
     if (n_tiles == 0) return 0;
     const int G = H / Hkv;
@@ -181,19 +197,20 @@ TK_API int tk_attn_generic(const void* q, const void* kv_pool, void* out, const 
     const int heads_per_chunk = min(G, BM / tokens_per_tile);
     TK_CHECK_ARG(heads_per_chunk >= 1, "attention: tile of %d tokens leaves no room for a head", tokens_per_tile);
     const int chunks = (G + heads_per_chunk - 1) / heads_per_chunk;
-    const size_t smem = attn_generic_smem(D);
+    const size_t smem = attn_generic_smem(D, Dv);
     dim3 grid(n_tiles, Hkv * chunks);
     if (dtype == TK_F32) {
         cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_generic_kernel<float>, dim3(grid), dim3(THREADS), smem, stream, 
             (const float*)q, (const float*)kv_pool, (float*)out, positions, tok_seq, block_table,
-            bt_stride, tile_tok0, tile_ntok, H, Hkv, D, P, window, scale, heads_per_chunk);
+            bt_stride, tile_tok0, tile_ntok, H, Hkv, D, Dv, Dp, P, window, keep_first, sink, round_p,
+            scale, heads_per_chunk);
     } else if (dtype == TK_BF16) {
         cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(THREADS), smem, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, (__nv_bfloat16*)out, positions,
-            tok_seq, block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, D, P, window, scale,
-            heads_per_chunk);
+            tok_seq, block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, D, Dv, Dp, P, window,
+            keep_first, sink, round_p, scale, heads_per_chunk);
     } else {
         TK_CHECK_ARG(false, "attention: unknown dtype %d", dtype);
     }

@@ -14,6 +14,7 @@ from pathlib import Path
 
 import torch
 
+from tokenomos_b200.models.darizen import Darizen
 from tokenomos_b200.models.lfm3 import Lfm3
 from tokenomos_b200.parts import build_model
 from tokenomos_b200.parts.registry import Runtime, Tuning
@@ -34,8 +35,10 @@ def register(arch) -> None:
 
 def architecture_of(raw_config: dict):
     names = raw_config.get("architectures") or raw_config.get("text_config", {}).get("architectures")
+    if not names and isinstance(raw_config.get("architecture"), str):
+        names = [raw_config["architecture"]]          # some folders name one architecture, not a list
     if not names:
-        raise ValueError("config.json has no 'architectures' entry")
+        raise ValueError("config.json has no 'architectures' (or 'architecture') entry")
     if names[0] not in ARCHS:
         raise ValueError(f"no declaration for {names[0]!r}; known: {sorted(ARCHS)}")
     return ARCHS[names[0]]
@@ -89,3 +92,4 @@ def from_tensors(conf: Configured, tensors: dict, device: torch.device | str = "
 
 
 register(Lfm3())
+register(Darizen())

@@ -15,7 +15,7 @@ from tokenomos_b200.ops._lib import BF16, F32, KernelError
 
 __all__ = [
     "KernelError", "available", "checks_enabled", "set_check_bounds", "checks_status", "gather_rows", "add_rmsnorm", "swiglu", "head_gate",
-    "qk_norm_rope_write", "attention", "attention_rows", "attention_mma_supported",
+    "qk_norm_rope_write", "rotary_write", "stream32_add_norm", "glu_clamped", "sigmoid_gate", "attention", "attention_rows", "attention_mma_supported",
     "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
     "attention_prefill_tc", "attention_prefill_tc_supported", "attention_prefill_tc_tokens",
     "attention_prefill_tc_status",
@@ -252,22 +252,126 @@ def attention_rows() -> int:
 def attention(q: torch.Tensor, kv_pool: torch.Tensor, positions: torch.Tensor,
               tok_seq: torch.Tensor, block_table: torch.Tensor, tile_tok0: torch.Tensor,
               tile_ntok: torch.Tensor, tokens_per_tile: int, window: int | None,
-              scale: float) -> torch.Tensor:
+              scale: float, keep_first: int = 0, sink: bool = False, v_dim: int | None = None,
+              round_p: bool = True) -> torch.Tensor:
     """Causal (optionally windowed) attention of ``q`` [T, H, D] over the paged cache
-    ``kv_pool`` [pages, 2, Hkv, P, D], which already holds this step's keys. Tiles name runs of
-    at most ``tokens_per_tile`` tokens of one sequence."""
+    ``kv_pool`` [pages, 2, Hkv, P, Dp], which already holds this step's keys. Tiles name runs of
+    at most ``tokens_per_tile`` tokens of one sequence. ``keep_first``: that many first positions
+    of a sequence stay visible behind the window; ``sink``: one is added to the softmax's
+    denominator; ``v_dim``: the values' size (default: the keys'; the cache rows hold at least
+    both); ``round_p``: the weights are rounded to the storage type before they meet the values
+    (the 16-bit reference's rounding) instead of staying 32-bit. Returns [T, H, v_dim]."""
     _cuda(q, kv_pool, positions, tok_seq, block_table, tile_tok0, tile_ntok)
     T, H, D = q.shape
-    _, two, Hkv, P, D2 = kv_pool.shape
-    if two != 2 or D2 != D or kv_pool.dtype != q.dtype or not (q.is_contiguous() and kv_pool.is_contiguous()):
+    _, two, Hkv, P, Dp = kv_pool.shape
+    Dv = D if v_dim is None else int(v_dim)
+    if two != 2 or Dp < max(D, Dv) or kv_pool.dtype != q.dtype or not (q.is_contiguous() and kv_pool.is_contiguous()):
         raise KernelError("attention: q / cache layouts do not match")
-    out = torch.empty_like(q)
+    out = torch.empty(T, H, Dv, dtype=q.dtype, device=q.device)
     _lib.call("tk_attn_generic", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
               block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
-              _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), tokens_per_tile, H, Hkv, D, P,
-              int(window or 0), float(scale), _dtype_code(q), _stream())
+              _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), tokens_per_tile, H, Hkv, D, Dv, Dp, P,
+              int(window or 0), int(keep_first), int(bool(sink)), int(bool(round_p)), float(scale),
+              _dtype_code(q), _stream())
     return out
+
+
+def rotary_write(qkv: torch.Tensor, kv_pool: torch.Tensor | None, freq: torch.Tensor, cs_mult: float,
+                 positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor | None,
+                 heads: int, kv_heads: int, head_dim: int, v_dim: int, page: int, interleaved: bool,
+                 v_is_k: bool) -> torch.Tensor:
+    """Rotate the q and k heads of ``qkv`` (rows of ``heads`` query heads and ``kv_heads`` key
+    heads of ``head_dim``, then, unless ``v_is_k``, ``kv_heads`` value heads of ``v_dim``) by
+    ``position * freq`` with cos and sin times ``cs_mult``, columns paired (2i, 2i+1) when
+    ``interleaved`` else (i, i + R/2), R = 2 len(freq). Returns q [T, H, head_dim]; keys and
+    values go into ``kv_pool`` [pages, 2, Hkv, P, Dp] at each token's position (``v_is_k``: the
+    value is the key as projected, not rotated). ``kv_heads`` 0: queries only."""
+    _cuda(qkv, kv_pool, freq, positions, tok_seq, block_table)
+    T = qkv.shape[0]
+    width = (heads + kv_heads) * head_dim + (0 if v_is_k else kv_heads * v_dim)
+    if qkv.stride(1) != 1 or qkv.shape[1] != width:
+        raise KernelError(f"rotary_write: qkv of width {qkv.shape[1]}, the heads need {width}")
+    rot = 2 * freq.numel()
+    _f32vec(freq, "freq", rot // 2)
+    q = torch.empty(T, heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    row = 0
+    if kv_heads:
+        if kv_pool is None or block_table is None:
+            raise KernelError("rotary_write: keys need a cache and a block table")
+        row = kv_pool.shape[-1]
+        if (kv_pool.dtype != qkv.dtype or not kv_pool.is_contiguous() or kv_pool.dim() != 5
+                or tuple(kv_pool.shape[1:4]) != (2, kv_heads, page) or row < max(head_dim, v_dim)):
+            raise KernelError(f"rotary_write: cache {tuple(kv_pool.shape)} {kv_pool.dtype} does not match "
+                              f"[pages, 2, {kv_heads}, {page}, >= {max(head_dim, v_dim)}] {qkv.dtype}")
+        _i32(block_table, "block_table")
+    _lib.call("tk_rotary_write", _ptr(qkv), qkv.stride(0), _ptr(q), _ptr(kv_pool), _ptr(freq), float(cs_mult),
+              _ptr(_i32(positions, "positions")), _ptr(_i32(tok_seq, "tok_seq")), _ptr(block_table),
+              block_table.stride(0) if block_table is not None else 0, T, heads, kv_heads, head_dim,
+              int(v_dim), int(row or max(head_dim, v_dim)), rot, page, int(bool(interleaved)), int(bool(v_is_k)),
+              _dtype_code(qkv), _stream())
+    return q
+
+
+def stream32_add_norm(stream: torch.Tensor | None, x: torch.Tensor | None, weight: torch.Tensor | None,
+                      eps: float, rows_add: torch.Tensor | None = None, vec_add: torch.Tensor | None = None,
+                      out_dtype: torch.dtype | None = None, in_place: bool = False):
+    """A residual stream kept in 32-bit: ``stream' = stream + x + rows_add + vec_add`` (each
+    optional, ``stream`` float32 [rows, width], ``x`` and ``rows_add`` in the model's storage type,
+    ``vec_add`` float32 [width]) and ``y = rmsnorm(stream') * weight`` in ``out_dtype`` (default: the
+    type of ``x`` / ``rows_add``), rounded once. Returns ``(y, stream')``; ``y`` is None without
+    ``weight``. ``in_place``: ``stream'`` overwrites ``stream``."""
+    _cuda(stream, x, weight, rows_add, vec_add)
+    ref = x if x is not None else (rows_add if rows_add is not None else stream)
+    if ref is None:
+        raise KernelError("stream32_add_norm: nothing to add up")
+    rows, width = ref.shape
+    store = out_dtype or (x.dtype if x is not None else (rows_add.dtype if rows_add is not None else torch.float32))
+    if stream is not None and (stream.dtype != torch.float32 or not stream.is_contiguous()
+                               or tuple(stream.shape) != (rows, width)):
+        raise KernelError("stream32_add_norm: the stream is a contiguous float32 [rows, width] tensor")
+    for name, t in (("x", x), ("rows_add", rows_add)):
+        if t is not None and (t.dtype != store or tuple(t.shape) != (rows, width) or t.stride(1) != 1):
+            raise KernelError(f"stream32_add_norm: {name} must be {store} [rows, width] with contiguous rows")
+    if rows_add is not None and not rows_add.is_contiguous():
+        raise KernelError("stream32_add_norm: rows_add must be contiguous")
+    w = _f32vec(weight, "norm weight", width)
+    v = _f32vec(vec_add, "vec_add", width)
+    y = torch.empty(rows, width, dtype=store, device=ref.device) if w is not None else None
+    out = stream if (in_place and stream is not None) else torch.empty(rows, width, dtype=torch.float32,
+                                                                    device=ref.device)
+    if store not in (torch.float32, torch.bfloat16):
+        raise KernelError(f"storage type {store} is not built (float32 and bfloat16 are)")
+    code = F32 if store == torch.float32 else BF16
+    _lib.call("tk_stream32_add_norm", _ptr(stream), _ptr(x), x.stride(0) if x is not None else 0, _ptr(rows_add),
+              _ptr(v), _ptr(w), float(eps), _ptr(out), _ptr(y), rows, width, code, _stream())
+    return y, out
+
+
+def glu_clamped(gu: torch.Tensor, limit: float | None, alpha: float, shift: float) -> torch.Tensor:
+    """``g * sigmoid(alpha g) * (u + shift)`` with ``g = min(gate, limit)``, ``u = clamp(up,
+    -limit, limit)`` for ``gu = [gate | up]`` of width ``2 I`` (``limit`` None: no clamp)."""
+    _cuda(gu)
+    if not gu.is_contiguous() or gu.shape[1] % 2:
+        raise KernelError("glu_clamped: input must be contiguous with an even width")
+    rows, inter = gu.shape[0], gu.shape[1] // 2
+    out = torch.empty(rows, inter, dtype=gu.dtype, device=gu.device)
+    _lib.call("tk_glu_clamped", _ptr(gu), _ptr(out), rows, inter, float(limit or 0.0), float(alpha), float(shift),
+              _dtype_code(gu), _stream())
+    return out
+
+
+def sigmoid_gate(x: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """In place: ``x[t, c] *= sigmoid(g[t, c])`` for ``x`` [T, C] contiguous; ``g`` [T, C] may be a
+    column block of a wider tensor."""
+    _cuda(x, g)
+    rows = g.shape[0]
+    width = x.numel() // max(rows, 1)
+    if not (x.is_contiguous() and g.dim() == 2 and g.stride(1) == 1 and g.dtype == x.dtype
+            and g.shape[1] == width and x.numel() == rows * width):
+        raise KernelError("sigmoid_gate: contiguous x [T, C], g [T, C] with contiguous rows, one storage type")
+    _lib.call("tk_sigmoid_gate", _ptr(x), _ptr(g), g.stride(0), rows, width, _dtype_code(x), _stream())
+    return x
 
 
 def attention_mma_supported(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:

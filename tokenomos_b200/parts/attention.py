@@ -6,6 +6,14 @@ rotary encoding; the new keys and values go into the cache; every query attends 
 optional per-head sigmoid gate from the same input; output projection
 (Tokenomos models/blocks/attention.py:225-259). ``kv_source``: the layer has queries only and
 reads the cache of another call of the layer list.
+
+Options beyond that, each a parameter: ``sink`` (one more term in the softmax's denominator, a
+key of score 0 without a value: ``p_j = exp(s_j) / (1 + sum exp(s_j))``); ``keep_first`` (with a
+window: the first positions of a sequence stay visible, at their true positions); ``v_dim``
+(value heads of another size than the keys); ``v_is_k`` (no value projection: a key as projected,
+before the position encoding, is its value); ``gate_kind`` "element" (the gate has one value
+per output element, not per head); ``exact`` (the softmax's weights stay 32-bit until they meet
+the values in kernels that do not need them in 16 bits).
 """
 
 from __future__ import annotations
@@ -25,10 +33,27 @@ class Attention:
                  eps: float, q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None,
                  window: int | None = None, scale: float | None = None,
                  gate: Linear | None = None, kv_source: int | None = None,
-                 gate_fused: bool = False, tuning: Tuning = DEFAULT_TUNING):
+                 gate_fused: bool = False, tuning: Tuning = DEFAULT_TUNING, sink: bool = False,
+                 keep_first: int = 0, v_dim: int | None = None, v_is_k: bool = False,
+                 gate_kind: str = "head", exact: bool = False):
         """``gate``: the per-head gate's projection as a part of its own; ``gate_fused``: its rows
         are the last of ``qkv``'s instead (after q, k, v, then zero rows up to a multiple of 8), so
         that one product yields both."""
+        v_dim = head_dim if v_dim is None else int(v_dim)
+        if v_is_k and (v_dim != head_dim or kv_source is not None):
+            raise ValueError("attention: values that are the keys have the keys' size and a cache of their own")
+        if gate_kind not in ("head", "element"):
+            raise ValueError(f"attention: gate kind {gate_kind!r}: 'head' or 'element'")
+        if keep_first and window is None:
+            raise ValueError("attention: kept first positions need a window")
+        if v_dim > ops.ATTENTION_MAX_HEAD_DIM:
+            raise ValueError(f"attention: a value size of {v_dim} is above the "
+                             f"{ops.ATTENTION_MAX_HEAD_DIM} the attention kernels take")
+        self.sink, self.keep_first, self.v_dim, self.v_is_k = bool(sink), int(keep_first), v_dim, bool(v_is_k)
+        self.gate_kind, self.exact = gate_kind, bool(exact)
+        # what only the general kernels compute (the fused and tensor-core forms take none of it)
+        self.extended = bool(self.sink or self.keep_first or self.v_is_k or v_dim != head_dim
+                             or gate_kind != "head" or self.exact)
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads over {kv_heads} KV heads")
         if head_dim > ops.ATTENTION_MAX_HEAD_DIM:
@@ -47,28 +72,31 @@ class Attention:
         self.scale = head_dim ** -0.5 if scale is None else float(scale)
         self.kv_source = kv_source
         own_kv = 0 if kv_source is not None else kv_heads
-        self.qkv_width = (heads + 2 * own_kv) * head_dim
+        self.qkv_width = (heads + own_kv) * head_dim + (0 if v_is_k else own_kv * v_dim)
         self.gate_fused = gate_fused
+        self.gate_width = heads if gate_kind == "head" else heads * v_dim
         if gate_fused and gate is not None:
             raise ValueError("attention: the gate is either fused into qkv or a projection of its own")
-        if qkv.out_features != self.qkv_width + (-(-heads // 8) * 8 if gate_fused else 0):
+        if qkv.out_features != self.qkv_width + (-(-self.gate_width // 8) * 8 if gate_fused else 0):
             raise ValueError("attention: the fused projection does not match the head counts")
         self.norm_folded = False
         self._fused_freqs = None        # the rotation's frequencies once asked for; False: not fusable
         self.head_layout = HeadLayout(heads, own_kv, head_dim, self.q_norm,
-                                      self.k_norm if own_kv else None, self.eps)
+                                      self.k_norm if own_kv else None, self.eps,
+                                      v_dim=v_dim, v_is_k=self.v_is_k)
 
     def state_specs(self) -> dict:
         if self.kv_source is not None:
             return {"kv": SharedState(self.kv_source, "kv")}
+        row = max(self.head_dim, self.v_dim)         # a cache row holds a key or a value
         if self.window is None:
-            return {"kv": PagedKV(self.kv_heads, self.head_dim)}
-        return {"kv": WindowKV(self.kv_heads, self.head_dim, self.window)}
+            return {"kv": PagedKV(self.kv_heads, row)}
+        return {"kv": WindowKV(self.kv_heads, row, self.window, self.keep_first)}
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T = x.shape[0]
         out = self._heads(self.qkv(x), x, ctx, call)
-        return self.o(out.view(T, self.heads * self.head_dim))
+        return self.o(out.view(T, self.heads * self.v_dim))
 
     def _heads(self, proj: torch.Tensor, x: torch.Tensor | None, ctx: StepContext, call: int) -> torch.Tensor:
         """From the fused projection's rows to the gated heads' outputs [T, H, D]."""
@@ -76,13 +104,14 @@ class Attention:
             return self._decode_fused(proj, ctx, call)
         n = self.qkv_width
         if self.gate_fused:
-            return self._core(proj[:, :n], ctx, call, proj[:, n:n + self.heads])
+            return self._core(proj[:, :n], ctx, call, proj[:, n:n + self.gate_width])
         return self._core(proj, ctx, call, self.gate(x) if self.gate is not None else None)
 
     # ---- the block's norm and residual add taken into the two products (parts.contract) ----
 
     def fold_norm(self, weight: torch.Tensor) -> bool:
-        if self.qkv.weight.dtype != torch.bfloat16 or not self.tuning.fuse_norms or self.gate is not None:
+        if (self.qkv.weight.dtype != torch.bfloat16 or not self.tuning.fuse_norms or self.gate is not None
+                or self.extended):
             return False
         self.qkv.fold_columns(weight)
         self.norm_folded = True
@@ -107,7 +136,7 @@ class Attention:
     def _fused_decode(self, ctx: StepContext) -> bool:
         """Whether this step's attention runs as one kernel: every sequence brings one token, the
         position encoding is a plain rotation that says so, and the kernel takes the shape."""
-        if not (self.decode_fused and ctx.host.decode_only and self.gate is None
+        if not (self.decode_fused and ctx.host.decode_only and self.gate is None and not self.extended
                 and ctx.n_tokens <= self.tuning.decode_fused_rows):
             return False
         if self._fused_freqs is None:
@@ -145,16 +174,19 @@ class Attention:
         own_kv = self.head_layout.kv_heads
         q = self.rope.encode_qk(qkv, ctx, self.head_layout, pool if own_kv else None,
                                 table if own_kv else None)
-        if ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim, q.dtype):
+        if not self.extended and ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim, q.dtype):
             return self._attend_mma(q, pool, table, ctx, gate)
         rows = ops.attention_rows()
         group = self.heads // self.kv_heads
         per_tile = max(1, rows // group)
         _, tok0, _, ntok = ctx.tiles(per_tile)
         out = ops.attention(q, pool, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
-                            self.window, self.scale)
-        if gate is not None:
-            ops.head_gate(out, gate, self.heads, self.head_dim)
+                            self.window, self.scale, self.keep_first, self.sink, self.v_dim,
+                            round_p=not self.exact)
+        if gate is not None and self.gate_kind == "head":
+            ops.head_gate(out, gate, self.heads, self.v_dim)
+        elif gate is not None:
+            ops.sigmoid_gate(out, gate)
         return out
 
     # whether prompt portions may take the tcgen05 kernel (TOKENOMOS_B200_ATTN_TC=0: never)
@@ -239,7 +271,16 @@ def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
     own = {k[len("position."):]: v for k, v in tensors.items() if k.startswith("position.")}
     rope = builder_of("position", rope_spec["kind"])(rope_spec["params"], own, rt)
     source = params.get("kv_source")
-    mats = [tensors["q"]] if source is not None else [tensors["q"], tensors["k"], tensors["v"]]
+    v_is_k = bool(params.get("v_is_k"))
+    names = ["q"] if source is not None else (["q", "k"] if v_is_k else ["q", "k", "v"])
+    mats = [tensors[n] for n in names]
+    # biases (role names ``q_bias`` ...): all of the projections that read the input or none
+    biases = [tensors.get(n + "_bias") for n in names]
+    if any(b is not None for b in biases):
+        biases = [b if b is not None else torch.zeros(m.shape[0], dtype=torch.float32, device=m.device)
+                  for b, m in zip(biases, mats)]
+    else:
+        biases = None
     gated = "gate" in tensors
     if gated:
         # the gate reads the same input as q, k, v: its rows join theirs (padded to whole
@@ -247,8 +288,12 @@ def build_attention(params: dict, tensors: dict, rt: Runtime) -> Attention:
         g = tensors["gate"]
         pad = -g.shape[0] % 8
         mats.append(torch.cat((g, g.new_zeros(pad, g.shape[1]))) if pad else g)
+        if biases is not None:
+            biases.append(torch.zeros(mats[-1].shape[0], dtype=torch.float32, device=g.device))
     return Attention(
-        Linear.fused(mats, tuning=rt.tuning), Linear(tensors["o"], tuning=rt.tuning), params["heads"],
-        params["kv_heads"], params["head_dim"], rope, params["eps"], tensors.get("q_norm"),
+        Linear.fused(mats, biases, tuning=rt.tuning), Linear(tensors["o"], tuning=rt.tuning), params["heads"],
+        params["kv_heads"], params["head_dim"], rope, params.get("eps", 0.0), tensors.get("q_norm"),
         tensors.get("k_norm"), params.get("window"), params.get("scale"), None, source,
-        gate_fused=gated, tuning=rt.tuning)
+        gate_fused=gated, tuning=rt.tuning, sink=params.get("sink", False),
+        keep_first=params.get("keep_first", 0), v_dim=params.get("v_dim"), v_is_k=v_is_k,
+        gate_kind=params.get("gate_kind", "head"), exact=params.get("exact", False))

@@ -35,7 +35,9 @@ class PreNormBlock:
         # returns stream + part(norm(stream)) with both the statistics and the add inside its
         # own kernels. Without post-norms only: they sit between the part and the add.
         self.eps_mixer = self.eps_ffn = None
-        if post_mixer is None and post_ffn is None:
+        if ffn is None and (pre_ffn is not None or post_ffn is not None):
+            raise ValueError("a block without a feed-forward has no norms around one")
+        if post_mixer is None and post_ffn is None and ffn is not None:
             self.pre_mixer, self.eps_mixer = self._fold(pre_mixer, mixer)
             self.pre_ffn, self.eps_ffn = self._fold(pre_ffn, ffn)
 
@@ -69,6 +71,8 @@ class PreNormBlock:
                 h, residual = residual, None
             x, residual = self.pre_mixer.add_norm(h, residual, pending)
             h = self.mixer.forward(x, ctx, call)
+        if self.ffn is None:             # the mixer's output is the block's
+            return h, residual, self.post_mixer
         if self.eps_ffn is not None and self.ffn.can_stream(rows):
             return None, self.ffn.forward_stream(self._stream(h, residual), self.eps_ffn), None
         if h is None:
@@ -79,16 +83,18 @@ class PreNormBlock:
 
 @register("block", "prenorm")
 def build_prenorm(parts: dict) -> PreNormBlock:
-    return PreNormBlock(parts["mixer"], parts["ffn"], parts["pre_mixer_norm"],
-                        parts["pre_ffn_norm"], parts.get("post_mixer_norm"),
+    return PreNormBlock(parts["mixer"], parts.get("ffn"), parts["pre_mixer_norm"],
+                        parts.get("pre_ffn_norm"), parts.get("post_mixer_norm"),
                         parts.get("post_ffn_norm"))
 
 
 class Stack:
     def __init__(self, embedding: torch.Tensor, blocks: list, order: list[LayerCall], final_norm,
                  head: Linear | None, tuning: Tuning = DEFAULT_TUNING, embed_scale: float | None = None,
-                 logit_softcap: float | None = None, suppress: tuple[int, ...] = ()):
+                 logit_softcap: float | None = None, suppress: tuple[int, ...] = (),
+                 extras: dict[str, torch.Tensor] | None = None):
         self.embedding = embedding
+        self.extras = {name: t.float().contiguous() for name, t in (extras or {}).items()}
         self.embed_scale = None if embed_scale is None else float(embed_scale)
         self.logit_softcap = None if logit_softcap is None else float(logit_softcap)
         if self.logit_softcap is not None and self.logit_softcap <= 0:
@@ -105,12 +111,21 @@ class Stack:
         self.tied = head is None
         self.vocab, self.width = embedding.shape
         self.dtype = embedding.dtype
+        if any(call.add is not None for call in self.order) and getattr(
+                final_norm, "stream_dtype", None) != torch.float32:
+            raise ValueError("the layer list adds to the stream between blocks, which is built for models "
+                             "whose norms keep the stream in 32-bit (rmsnorm32)")
         for i, call in enumerate(self.order):
             if not 0 <= call.block < len(blocks):
                 raise ValueError(f"layer list entry {i} names block {call.block} of {len(blocks)}")
             if call.state_from is not None and not 0 <= call.state_from < i:
                 raise ValueError(f"layer list entry {i} reads the state of entry {call.state_from}, "
                                  "which must come earlier in the list")
+            if call.add is not None and call.add.tensor is not None:
+                t = self.extras.get(call.add.tensor)
+                if t is None or t.dim() != 2 or t.shape[1] != self.width or not 0 <= call.add.row < t.shape[0]:
+                    raise ValueError(f"layer list entry {i} adds row {call.add.row} of {call.add.tensor!r}, "
+                                     f"which is not a row of a [rows, {self.width}] stack tensor")
 
     @property
     def capture_safe(self) -> bool:
@@ -154,9 +169,24 @@ class Stack:
         """Runs the layer list; returns ``(h, residual, pending)`` of the last block: the final
         norm takes the last add with it, on the wanted rows only (``logits``)."""
         residual, pending = None, None
+        embedded = h
         for i, call in enumerate(self.order):
+            if call.add is not None:
+                h, residual = self._add_to_stream(call.add, embedded, h, residual, pending), None
+                pending = None
             h, residual, pending = self.blocks[call.block].forward(h, residual, pending, ctx, i)
         return h, residual, pending
+
+    def _add_to_stream(self, add, embedded, h, residual, pending) -> torch.Tensor:
+        """The stream (32-bit) with the pending output ``h``, and what ``add`` names, in it."""
+        if pending is not None:
+            raise ValueError("a post-norm is pending where the layer list adds to the stream")
+        vec = self.extras[add.tensor][add.row] if add.tensor is not None else None
+        rows = embedded if add.embedding else None
+        if h is None and rows is None:
+            h = torch.zeros_like(embedded)           # only a vector to add: the kernel wants rows
+        return ops.stream32_add_norm(residual, h, None, 0.0, rows_add=rows, vec_add=vec,
+                                     out_dtype=self.dtype)[1]
 
     def logits(self, out, rows: torch.Tensor | None) -> torch.Tensor:
         """Float32 logits [len(rows), vocab] at token rows ``rows`` (int32) of the step; None:

@@ -9,8 +9,10 @@ the context. (Counterpart in the reference: Tokenomos models/contract.py:19-137.
 State memory comes in two shapes:
 
 - paged, growing with the sequence: ``PagedKV`` (every position kept) and ``WindowKV`` (only the
-  last ``window`` positions are ever read, pages behind the window are given back). Specs with
-  equal ``group`` share one pool's page numbering and one block table per request;
+  last ``window`` positions are ever read, and with ``keep_first`` the first positions of the
+  sequence as well; pages behind the window, but for those that hold kept positions, are given
+  back). Specs with equal ``group`` share one pool's page numbering and one block table per
+  request;
 - fixed size per request: ``SlotState``, a row ``[*shape]`` of a ``[slots, *shape]`` tensor,
   row 0 being the null row that padded sequences point at. A request that starts at position
   0 must read its row as zeros: parts check ``seq_ctx == 0`` (or positions) instead of relying
@@ -21,7 +23,8 @@ State memory comes in two shapes:
 A spec says what the cache manager has to do for it through three attributes, so a part may
 bring a spec class of its own: ``storage`` (``"paged"``, ``"slot"`` or ``"shared"``); for paged
 storage ``group`` (specs with equal groups share page numbers and block tables), ``window``
-(None: every position is kept) and ``page_shape(page_size)`` (the shape of one page); for slot
+(None: every position is kept), optionally ``keep_first`` (positions at the start of a sequence
+that a window never passes) and ``page_shape(page_size)`` (the shape of one page); for slot
 storage ``shape`` and ``dtype``; for shared storage ``source`` and ``name``.
 
 Captured steps. With ``graphs=True`` the engine records a step's kernels once per shape and
@@ -61,16 +64,19 @@ class PagedKV:
 
 @dataclass(frozen=True)
 class WindowKV:
-    """Keys and values of which only the last ``window`` positions are read."""
+    """Keys and values of which only the last ``window`` positions are read, and the first
+    ``keep_first`` of the sequence. ``head_dim``: the width of a cache row (the larger of the
+    key and value sizes where they differ)."""
 
     kv_heads: int
     head_dim: int
     window: int
+    keep_first: int = 0
     storage = "paged"
 
     @property
     def group(self) -> tuple:
-        return ("window", self.window)
+        return ("window", self.window, self.keep_first) if self.keep_first else ("window", self.window)
 
     def page_shape(self, page_size: int) -> tuple[int, ...]:
         return (2, self.kv_heads, page_size, self.head_dim)
@@ -213,7 +219,9 @@ class HeadLayout:
     """What a position encoding needs to know of the projection it is handed: ``qkv`` rows hold
     ``heads`` query heads, then ``kv_heads`` key heads, then ``kv_heads`` value heads, each of
     ``head_dim`` (``kv_heads`` 0: queries only); the per-head norm weights (float32 [head_dim] or
-    None) and eps that go with them."""
+    None) and eps that go with them. ``v_dim``: the value heads' size when it is not the keys'.
+    ``v_is_k``: the rows hold no value heads; a key as projected (before norm and position) is
+    also its value."""
 
     heads: int
     kv_heads: int
@@ -221,6 +229,8 @@ class HeadLayout:
     q_norm: torch.Tensor | None
     k_norm: torch.Tensor | None
     eps: float
+    v_dim: int | None = None
+    v_is_k: bool = False
 
 
 @runtime_checkable

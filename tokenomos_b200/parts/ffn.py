@@ -74,3 +74,32 @@ def build_swiglu(params: dict, tensors: dict, rt: Runtime) -> SwiGLU:
     if gate.dtype == torch.bfloat16 and gate.shape[0] % RUN == 0:
         return SwiGLU(Linear(interleave_rows(gate, up, RUN), tuning=rt.tuning), down, RUN)
     return SwiGLU(Linear.fused([gate, up], tuning=rt.tuning), down)
+
+
+class ClampedGLU:
+    """Gated feed-forward with clamped branches: ``g = min(gate(x), limit)``, ``u = clamp(up(x),
+    -limit, limit)``, ``down(g * sigmoid(alpha g) * (u + shift))``; gate and up are one fused
+    projection (gate first), every projection may have a bias. ``limit`` None: no clamp."""
+
+    capture_safe = True
+
+    def __init__(self, gate_up: Linear, down: Linear, limit: float | None, alpha: float = 1.0,
+                 shift: float = 0.0):
+        if gate_up.out_features != 2 * down.in_features:
+            raise ValueError("ClampedGLU: gate_up must be twice as wide as down's input")
+        if limit is not None and limit <= 0:
+            raise ValueError(f"ClampedGLU: a limit of {limit}: it must be positive")
+        self.gate_up, self.down = gate_up, down
+        self.limit, self.alpha, self.shift = limit, float(alpha), float(shift)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down(ops.glu_clamped(self.gate_up(x), self.limit, self.alpha, self.shift))
+
+
+@register("feed_forward", "glu_clamped")
+def build_clamped_glu(params: dict, tensors: dict, rt: Runtime) -> ClampedGLU:
+    biases = [tensors.get("gate_bias"), tensors.get("up_bias")]
+    gate_up = Linear.fused([tensors["gate"], tensors["up"]], biases if biases[0] is not None else None,
+                           tuning=rt.tuning)
+    return ClampedGLU(gate_up, Linear(tensors["down"], tensors.get("down_bias"), tuning=rt.tuning),
+                      params.get("limit"), params.get("alpha", 1.0), params.get("shift", 0.0))

@@ -42,3 +42,40 @@ class RMSNorm:
 @register("norm", "rmsnorm")
 def build_rmsnorm(params: dict, tensors: dict, rt: Runtime) -> RMSNorm:
     return RMSNorm(tensors["weight"], params["eps"])
+
+
+class StreamNorm32:
+    """RMSNorm over a residual stream that is kept in 32-bit whatever the model's storage type.
+
+    ``stream' = stream + x`` is formed and kept in float32; ``y = stream' / sqrt(mean(stream'^2) +
+    eps) * (offset + w)`` is computed in 32-bit and rounded once to the storage type of the
+    projections that read it. ``offset`` 1: a weight stored around zero. The block arrangements
+    call ``add_norm`` like any other norm's; the stream they carry between blocks is then a
+    float32 tensor, and ``x`` (a part's output still to be added) is in the storage type."""
+
+    capture_safe = True
+    stream_dtype = torch.float32
+
+    def __init__(self, weight: torch.Tensor, eps: float, offset: float = 0.0,
+                 store: torch.dtype = torch.float32):
+        self.weight = (weight.float() + float(offset)).contiguous()
+        self.eps = float(eps)
+        self.width = weight.numel()
+        self.store = store
+
+    def add_norm(self, x: torch.Tensor, residual: torch.Tensor | None, pre=None):
+        """``stream = residual + x``; returns ``(norm(stream), stream)``. ``x`` alone may be the
+        stream itself (float32 in a 16-bit model) or the rows that start one."""
+        if pre is not None:
+            raise ValueError("StreamNorm32: no post-norm can be taken into the add")
+        if residual is None and x.dtype == torch.float32 and self.store != torch.float32:
+            return ops.stream32_add_norm(x, None, self.weight, self.eps, out_dtype=self.store, in_place=True)
+        return ops.stream32_add_norm(residual, x, self.weight, self.eps, out_dtype=self.store)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return self.add_norm(x, None)[0]
+
+
+@register("norm", "rmsnorm32")
+def build_stream_norm32(params: dict, tensors: dict, rt: Runtime) -> StreamNorm32:
+    return StreamNorm32(tensors["weight"], params["eps"], params.get("offset", 0.0), rt.dtype)

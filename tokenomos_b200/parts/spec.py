@@ -54,12 +54,26 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class StreamAdd:
+    """Something added to the residual stream right before an entry of the layer list runs:
+    the embedding output (the stream as it was before the first entry) if ``embedding``, then row
+    ``row`` of the stack tensor ``tensor`` (a name of ``ModelSpec.extras``; None: nothing). Both
+    join the stream's 32-bit sum."""
+
+    embedding: bool = False
+    tensor: str | None = None
+    row: int = 0
+
+
+@dataclass(frozen=True)
 class LayerCall:
     """One entry of the layer list: run block ``block``; ``state_from`` names an earlier entry
-    of the list whose state this one reads instead of owning one (None: its own)."""
+    of the list whose state this one reads instead of owning one (None: its own); ``add``: what
+    joins the stream before the block runs (a looped stack re-feeds its input this way)."""
 
     block: int
     state_from: int | None = None
+    add: StreamAdd | None = None
 
 
 @dataclass(frozen=True)
@@ -81,6 +95,8 @@ class ModelSpec:
     embed_scale: float | None = None
     logit_softcap: float | None = None
     suppress: tuple[int, ...] = ()
+    # tensors of the stack itself (not of a block), by the name ``StreamAdd.tensor`` uses
+    extras: tuple[tuple[str, TensorDecl], ...] = ()
 
     def tensor_decls(self) -> list[TensorDecl]:
         """Every tensor the model reads, in a fixed order (the order random weights are drawn)."""
@@ -89,6 +105,7 @@ class ModelSpec:
             for part in block.parts.values():
                 if part is not None:
                     out.extend(part.tensors.values())
+        out.extend(decl for _, decl in self.extras)
         out.extend(self.final_norm.tensors.values())
         if self.head is not None:
             out.append(self.head)

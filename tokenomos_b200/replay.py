@@ -32,7 +32,7 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (sizes the page pool)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-requests", type=int, default=8, help="live requests (state slots)")
+    ap.add_argument("--max-requests", type=int, default=4, help="live requests (state slots)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
