@@ -1,0 +1,620 @@
+"""The Darizen decoder against its plain implementation (``plain_darizen``): every mechanism
+alone, the whole model replayed four ways in 32-bit and in bfloat16 on poisoned pools, edges of
+windows, kept first positions and pages with one loud key, long decoding, generation through the
+entry points. The configurations here are made for the tests: sizes that are no powers of two,
+value heads of another size than the keys, groups of one, a loop that runs once, a layer without
+a feed-forward, windows shorter than a page and longer than any request."""
+
+from __future__ import annotations
+
+import json
+import math
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import plain_darizen as plain
+import trace_util
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def att(heads, kv_heads, dim, window, dims=None, scaling=None, base=10000.0, scale=None):
+    rot = {"base": base, "dims": dims or dim}
+    if scaling:
+        rot["scaling"] = scaling
+    return {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim,
+                                           "scale": scale or dim ** -0.5, "mask": {"size": window}, "rot": rot}}
+
+
+def att2(heads, kv_heads, dim, vdim, window, keep_first=None, dims=None, factor=None, base=10000.0, scale=None):
+    rot = {"base": base, "dims": dims or dim}
+    if factor:
+        rot["scaling"] = {"factor": factor}
+    mask = {"size": window}
+    if keep_first is not None:
+        mask["keep_first"] = keep_first
+    return {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+                                             "scale": scale or dim ** -0.5, "mask": mask, "rot": rot}}
+
+
+def mlp(ff, limit):
+    return {"kind": "dense", "ff": ff, "limit": limit}
+
+
+YARN = {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}
+
+# A: a loop from the first layer on, partial rotation, a group of one, values wider than keys, a
+#    layer without a feed-forward, windows that no page size divides
+DZ_A = {"architecture": "Darizen", "vocab": 320, "width": 64, "norm": {"eps": 1e-5},
+        "layers": [dict(att(4, 4, 16, 9, dims=8, scaling=YARN), mlp=mlp(96, 0.8)),
+                   dict(att2(6, 2, 16, 24, 13, keep_first=3, factor=2.0), mlp=None),
+                   dict(att2(2, 1, 32, 8, 40, dims=32), mlp=mlp(48, 2.0))],
+        "loop": {"start": 0, "stop": 2, "times": 2}}
+# B: kept positions over several pages, a window of one page and one of a single position, a
+#    window longer than any request, a loop that runs once
+DZ_B = {"architecture": "Darizen", "vocab": 200, "width": 96, "norm": {"eps": 1e-6},
+        "layers": [dict(att2(4, 1, 24, 24, 16, keep_first=20, factor=8.0, base=500.0), mlp=mlp(80, 1.5)),
+                   dict(att(3, 3, 8, 1, scaling={"factor": 2.0, "original": 32, "fast": 32.0, "slow": 1.0}),
+                        mlp=mlp(64, 1.0)),
+                   dict(att2(2, 2, 12, 20, 500, keep_first=1), mlp=mlp(40, 3.0))],
+        "loop": {"start": 1, "stop": 2, "times": 1}}
+# C: no loop at all, one layer, one head
+DZ_C = {"architecture": "Darizen", "vocab": 128, "width": 32, "norm": {"eps": 1e-5},
+        "layers": [dict(att(1, 1, 16, 64), mlp=mlp(32, 5.0))]}
+# D: head sizes the tensor-core attention kernels take in bfloat16 (64 and 128), groups of four
+#    and two, windows over several pages, kept positions, a loop of three passes
+DZ_D = {"architecture": "Darizen", "vocab": 400, "width": 128, "norm": {"eps": 1e-5},
+        "layers": [dict(att2(8, 2, 64, 64, 40, keep_first=5, factor=4.0), mlp=mlp(160, 1.5)),
+                   dict(att(4, 2, 128, 24, dims=64, scaling={"factor": 2.0, "original": 128, "fast": 16.0,
+                                                             "slow": 1.0}), mlp=mlp(96, 1.5)),
+                   dict(att(8, 2, 64, 70), mlp=None)],
+        "loop": {"start": 1, "stop": 3, "times": 3}}
+
+CASES = {
+    "A": dict(config=DZ_A, seed=11, page=4, lengths=[1, 2, 7, 30, 61, 45]),
+    "B": dict(config=DZ_B, seed=12, page=8, lengths=[3, 19, 21, 50, 90, 33]),
+    "C": dict(config=DZ_C, seed=13, page=16, lengths=[1, 5, 64, 65, 140]),
+    "D": dict(config=DZ_D, seed=14, page=16, lengths=[2, 31, 150, 65, 200, 90]),
+}
+# Bounds relative to the request's largest |logit|, about twice what a B200 measured. Against
+# the float64 plain implementation, 32-bit: A 2.2e-6, B 1.9e-6, C 1.7e-6, D 1.4e-5 (D runs its
+# loud layers three times); bfloat16: A 2.2 %, B 2.3 %, C 3.4 %, D 10 %. Between two ways of
+# cutting the same run, 32-bit: at most 6.7e-6; bfloat16: A 0.18 %, B 0.3 %, C 1e-7, D 1.7 %
+# (a decoded token and a prompt portion round alike but for the attention kernels' tiling).
+TOL_F32 = {"A": 1e-5, "B": 1e-5, "C": 1e-5, "D": 4e-5}
+TOL_F32_SAME = {"A": 5e-6, "B": 5e-6, "C": 2e-6, "D": 2e-5}
+TOL_BF16 = {"A": 4.5e-2, "B": 4.5e-2, "C": 6e-2, "D": 0.2}
+TOL_BF16_SAME = {"A": 4e-3, "B": 6e-3, "C": 1e-3, "D": 3.5e-2}
+
+
+def make_tensors(config: dict, seed: int) -> dict[str, torch.Tensor]:
+    """Random weights, rounded to bfloat16. Queries and keys are loud (scores spread over many
+    units, so that one key more or less behind a window's edge, or a missing sink, moves the
+    logits far beyond rounding); norm weights and biases are far from zero."""
+    from tokenomos_b200 import models
+    from tokenomos_b200.weights.random_init import random_tensors
+
+    arch = models.architecture_of(config)
+    spec = arch.declare(arch.config_class.from_dict(config))
+    tensors = random_tensors(spec.tensor_decls(), seed, std=1.0)
+    width = config["width"]
+    out = {}
+    for name, t in tensors.items():
+        if name.endswith((".mix.q", ".mix.k")):
+            t = t * (2.5 / math.sqrt(width))
+        elif name.endswith(".b") or "norm" in name or name == "loop.step":
+            t = t * 0.3
+        elif name == "embed":
+            t = t * 1.0
+        else:
+            t = t / math.sqrt(t.shape[-1])
+        out[name] = t.to(torch.bfloat16)
+    return out
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    from safetensors.torch import save_file
+
+    out = {}
+    for name, case in CASES.items():
+        folder = tmp_path_factory.mktemp(f"dz_{name}")
+        tensors = make_tensors(case["config"], case["seed"])
+        (folder / "config.json").write_text(json.dumps(case["config"]))
+        save_file({k: v.contiguous() for k, v in tensors.items()}, str(folder / "model.safetensors"))
+        out[name] = (folder, {k: v.double() for k, v in tensors.items()})
+    return out
+
+
+def requests_for(name: str) -> dict[str, list[int]]:
+    g = torch.Generator().manual_seed(77 + ord(name))
+    vocab = CASES[name]["config"]["vocab"]
+    return {f"r{i}": torch.randint(0, vocab, (n,), generator=g).tolist()
+            for i, n in enumerate(CASES[name]["lengths"])}
+
+
+def compare(got: dict, want: dict, tol: float, what: str):
+    for rid, ref in want.items():
+        assert got[rid].shape == ref.shape, (what, rid, got[rid].shape, ref.shape)
+        assert torch.isfinite(got[rid]).all(), (what, rid)
+        err = (got[rid] - ref).abs().amax(dim=1)
+        scale = ref.abs().max().item()
+        bad = (err > tol * scale).nonzero()
+        assert bad.numel() == 0, (f"{what}: request {rid}: first wrong position {int(bad[0])} of {len(err)}: "
+                                  f"error {err[int(bad[0])].item():.3e}, allowed {tol * scale:.3e}")
+
+
+# ---------------------------------------------------------------------------------------------
+# without a GPU: configuration, declaration, the cache manager's kept pages, the rotary table
+# ---------------------------------------------------------------------------------------------
+
+def test_configuration_reads_every_size_and_lists_every_fault():
+    from tokenomos_b200.config import ConfigError, DarizenConfig
+
+    cfg = DarizenConfig.from_dict(DZ_A)
+    assert (cfg.vocab, cfg.width, cfg.norm_eps) == (320, 64, 1e-5)
+    m = cfg.layers[1].mixer
+    assert (m.kind, m.heads, m.kv_heads, m.dim, m.vdim, m.window, m.keep_first) == ("attention_2", 6, 2, 16, 24, 13, 3)
+    assert m.rot.scaling == {"kind": "linear", "factor": 2.0}
+    assert cfg.layers[0].mixer.rot.scaling["kind"] == "yarn" and cfg.layers[0].mixer.keep_first == 0
+    assert cfg.layers[2].mixer.rot.scaling is None and cfg.layers[2].mixer.keep_first == 0
+    assert cfg.layers[1].mlp is None and cfg.layers[2].mlp.limit == 2.0
+    assert (cfg.loop.start, cfg.loop.stop, cfg.loop.times) == (0, 2, 2)
+    assert DarizenConfig.from_dict(DZ_C).loop is None
+    bad = json.loads(json.dumps(DZ_A))
+    bad["layers"][0]["mixer"]["kv_heads"] = 3
+    bad["layers"][1]["mixer"]["rot"]["dims"] = 7
+    bad["layers"][2]["mlp"]["kind"] = "sparse"
+    bad["loop"]["stop"] = 9
+    del bad["width"]
+    with pytest.raises(ConfigError) as e:
+        DarizenConfig.from_dict(bad)
+    for part in ("4 heads over 3", "dims = 7", "'sparse'", "loop", "'width'"):
+        assert part in str(e.value), part
+
+
+def test_declaration_lists_the_layer_runs_and_the_tensors():
+    from tokenomos_b200 import models
+
+    arch = models.architecture_of(DZ_D)
+    spec = arch.declare(arch.config_class.from_dict(DZ_D))
+    assert [c.block for c in spec.order] == [0, 1, 2, 1, 2, 1, 2]
+    assert [(c.add.embedding, c.add.row) if c.add else None for c in spec.order] == [
+        None, (False, 0), None, (True, 1), None, (True, 2), None]
+    assert [(i, t) for i, t in plain.layer_runs(DZ_D)] == [(0, None), (1, 0), (2, None), (1, 1), (2, None),
+                                                           (1, 2), (2, None)]
+    names = {d.name: d.shape for d in spec.tensor_decls()}
+    assert names["loop.step"] == (3, 128) and names["l0.mix.v"] == (128, 128) and names["l0.mix.q.b"] == (512,)
+    assert "l1.mix.v" not in names and "l1.mix.q.b" not in names and "l2.norm2" not in names
+    assert names["l1.mix.g"] == (512, 128) and names["l1.mlp.down.b"] == (128,) and names["head"] == (400, 128)
+    # no loop: no stack tensor, the layers once
+    spec = arch.declare(arch.config_class.from_dict(DZ_C))
+    assert [c.block for c in spec.order] == [0] and not spec.extras
+    # a loop from the first layer: the first pass adds its row, not the embedding
+    spec = arch.declare(arch.config_class.from_dict(DZ_A))
+    assert [(c.block, bool(c.add)) for c in spec.order] == [(0, True), (1, False), (0, True), (1, False), (2, False)]
+    assert (spec.order[0].add.embedding, spec.order[2].add.embedding) == (False, True)
+
+
+def test_kept_first_pages_stay_and_the_rest_come_back():
+    from tokenomos_b200.cache.manager import CacheManager
+    from tokenomos_b200.parts.contract import WindowKV
+
+    specs = {(0, "kv"): WindowKV(1, 8, window=6, keep_first=5), (1, "kv"): WindowKV(1, 8, window=6)}
+    cache = CacheManager(specs, page_size=4, num_pages=12, max_requests=2, dtype=torch.float32, device="meta")
+    kept, plain_group = ("window", 6, 5), ("window", 6)
+    cache.admit("a")
+    for _ in range(10):
+        cache.extend("a", 3)
+        cache.commit("a", 3)
+        cache.check()
+    st = cache.requests["a"]
+    # 30 tokens: the next query (position 30) sees from 25, i.e. from block 6; blocks 0 and 1 hold
+    # the five kept positions
+    assert [bool(p) for p in st.tables[kept]] == [True, True, False, False, False, False, True, True]
+    assert [bool(p) for p in st.tables[plain_group]] == [False] * 6 + [True, True]
+    assert cache.free_pages(kept) == 11 - 4 and cache.free_pages(plain_group) == 11 - 2
+    cache.release("a")
+    cache.check()
+    assert cache.free_pages(kept) == 11 and cache.free_slots() == 2
+    # the pages are handed out again, lowest first
+    cache.admit("b")
+    cache.extend("b", 9)
+    assert cache.block_table("b", kept) == [1, 2, 3]
+
+
+def test_rotary_table_matches_the_plain_one():
+    from tokenomos_b200.parts.rope import Rotary
+
+    for kind, rot in (("attention", {"base": 1e6, "dims": 48, "scaling": {"factor": 3.0, "original": 512,
+                                                                           "fast": 24.0, "slow": 1.5}}),
+                      ("attention", {"base": 1e4, "dims": 8, "scaling": YARN}),
+                      ("attention_2", {"base": 5e5, "dims": 32, "scaling": {"factor": 8.0}}),
+                      ("attention_2", {"base": 100.0, "dims": 6})):
+        want, mult = plain.rotary_table(kind, rot)
+        sc = rot.get("scaling")
+        scaling = None if sc is None else dict(sc, kind="yarn" if kind == "attention" else "linear")
+        got, got_mult = Rotary.table(rot["dims"], rot["base"], scaling)
+        assert torch.allclose(torch.tensor(got, dtype=torch.float64), want, rtol=1e-13, atol=0)
+        assert abs(got_mult - mult) < 1e-15
+    # the ramp really has all three regions in the first table
+    f, _ = plain.rotary_table("attention", {"base": 1e6, "dims": 48, "scaling": {
+        "factor": 3.0, "original": 512, "fast": 24.0, "slow": 1.5}})
+    base = torch.tensor([1e6 ** (-2.0 * i / 48) for i in range(24)], dtype=torch.float64)
+    ratio = f / base
+    assert ratio[0] == 1.0 and abs(ratio[-1] - 1 / 3) < 1e-12 and ((ratio < 0.99) & (ratio > 0.34)).any()
+
+
+def test_sink_softmax_of_the_plain_implementation_sums_below_one():
+    q = torch.randn(5, 2, 4, dtype=torch.float64)
+    k = torch.randn(5, 1, 4, dtype=torch.float64)
+    ones = torch.ones(5, 1, 3, dtype=torch.float64)
+    out = plain.sink_softmax_attention(q, k, ones, 0.5, plain.visible(5, 5))
+    s = (q[:, 0] @ k[:, 0].T * 0.5).masked_fill(~plain.visible(5, 5), float("-inf"))
+    want = torch.exp(s).sum(-1) / (1 + torch.exp(s).sum(-1))
+    assert torch.allclose(out[:, 0, 0], want, rtol=1e-12)
+    assert (out < 1).all()
+
+
+# ---------------------------------------------------------------------------------------------
+# each mechanism alone, on the GPU
+# ---------------------------------------------------------------------------------------------
+
+def dev(t, dtype=torch.float32):
+    return t.to(device="cuda", dtype=dtype).contiguous()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [24, 200, 2048, 2500])
+def test_stream_norm(dtype, width):
+    from tokenomos_b200 import ops
+
+    rows = 5
+    stream = torch.randn(rows, width) * 3
+    x = (torch.randn(rows, width)).to(dtype)
+    emb = torch.randn(rows, width).to(dtype)
+    vec = torch.randn(width)
+    w = torch.randn(width) * 0.3
+    y, new = ops.stream32_add_norm(dev(stream), dev(x, dtype), dev(w + 1.0), 1e-5, rows_add=dev(emb, dtype),
+                                   vec_add=dev(vec))
+    want_stream = ((stream + x.float()) + emb.float()) + vec
+    assert new.dtype == torch.float32 and torch.equal(new.cpu(), want_stream)
+    want = plain.unit_offset_rms_norm(want_stream.double(), w.double(), 1e-5)
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert y.dtype == dtype
+    assert (y.cpu().double() - want).abs().max() <= tol * want.abs().max()
+    # the stream alone, started from rows in the storage type
+    y2, s2 = ops.stream32_add_norm(None, dev(x, dtype), dev(w + 1.0), 1e-5)
+    assert torch.equal(s2.cpu(), x.float())
+    want2 = plain.unit_offset_rms_norm(x.double(), w.double(), 1e-5)
+    assert (y2.cpu().double() - want2).abs().max() <= tol * want2.abs().max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_clamped_glu_and_sigmoid_gate(dtype):
+    from tokenomos_b200 import ops
+
+    rows, inter = 7, 37
+    gu = (torch.randn(rows, 2 * inter) * 3).to(dtype)
+    for limit, alpha, shift in ((1.5, 1.702, 1.0), (0.25, 1.0, 0.0), (None, 2.0, 0.5)):
+        got = ops.glu_clamped(dev(gu, dtype), limit, alpha, shift).cpu().double()
+        g, u = gu[:, :inter].double(), gu[:, inter:].double()
+        if limit is not None:
+            g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
+        want = g * torch.sigmoid(alpha * g) * (u + shift)
+        tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+        assert (got - want).abs().max() <= tol * want.abs().max()
+    assert (gu.double().abs() > 1.5).any()           # the clamp was at work
+    x = torch.randn(rows, 3, 10).to(dtype)
+    wide = torch.randn(rows, 50).to(dtype)
+    got = ops.sigmoid_gate(dev(x, dtype), dev(wide, dtype)[:, 11:41]).cpu().double()
+    want = x.double().reshape(rows, 30) * torch.sigmoid(wide[:, 11:41].double())
+    tol = 1e-6 if dtype == torch.float32 else 2 ** -8
+    assert (got.reshape(rows, 30) - want).abs().max() <= tol * want.abs().max()
+
+
+class PagedSequence:
+    """One sequence's keys and values in a poisoned paged pool with shuffled page numbers, fed
+    through the framework's rotary and attention kernels portion by portion."""
+
+    def __init__(self, H, G, Dk, Dv, page, length, dtype, rotary, v_is_k, seed=0):
+        self.H, self.G, self.Dk, self.Dv, self.P, self.dtype = H, G, Dk, Dv, page, dtype
+        self.rotary, self.v_is_k = rotary, v_is_k
+        blocks = -(-length // page)
+        gen = torch.Generator().manual_seed(seed)
+        pages = (torch.randperm(blocks + 3, generator=gen)[:blocks] + 1).to(torch.int32)
+        self.table = pages.view(1, blocks).cuda()
+        self.pool = torch.full((blocks + 5, 2, G, page, max(Dk, Dv)), float("nan"), dtype=dtype, device="cuda")
+
+    def feed(self, q, k, v, a, b, window, keep_first, sink, scale):
+        """Positions ``a .. b-1``: rotate, write, attend; returns [b - a, H, Dv]."""
+        from tokenomos_b200 import ops
+
+        n = b - a
+        parts = [q[a:b].reshape(n, -1), k[a:b].reshape(n, -1)]
+        if not self.v_is_k:
+            parts.append(v[a:b].reshape(n, -1))
+        rows = dev(torch.cat(parts, dim=1), self.dtype)
+        positions = torch.arange(a, b, dtype=torch.int32, device="cuda")
+        seq = torch.zeros(n, dtype=torch.int32, device="cuda")
+        freq, mult, interleaved = self.rotary
+        qr = ops.rotary_write(rows, self.pool, dev(freq), mult, positions, seq, self.table, self.H, self.G,
+                              self.Dk, self.Dv, self.P, interleaved, self.v_is_k)
+        per_tile = max(1, ops.attention_rows() // (self.H // self.G))
+        tok0 = torch.arange(0, n, per_tile, dtype=torch.int32, device="cuda")
+        ntok = torch.clamp(n - tok0, max=per_tile).to(torch.int32)
+        return ops.attention(qr, self.pool, positions, seq, self.table, tok0, ntok, per_tile, window, scale,
+                             keep_first, sink, self.Dv, round_p=False).cpu().double()
+
+
+def cuts_of(T: int, how: str) -> list[int]:
+    if how == "whole":
+        return [0, T]
+    if how == "decode":
+        return [0, T // 2] + list(range(T // 2 + 1, T + 1))
+    cuts, sizes, k = [0], (5, 2, 13, 3, 2, 29), 0
+    while cuts[-1] < T:
+        cuts.append(min(T, cuts[-1] + sizes[k % len(sizes)]))
+        k += 1
+    return cuts
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("how", ["whole", "decode", "portions"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", [
+    dict(H=4, G=2, Dk=16, Dv=16, page=4, window=9, keep=0, interleaved=True, v_is_k=True, dims=8),
+    dict(H=6, G=2, Dk=16, Dv=24, page=8, window=13, keep=3, interleaved=False, v_is_k=False, dims=8),
+    dict(H=2, G=2, Dk=24, Dv=8, page=16, window=16, keep=20, interleaved=False, v_is_k=False, dims=12),
+    dict(H=3, G=1, Dk=8, Dv=8, page=4, window=1, keep=0, interleaved=True, v_is_k=True, dims=8),
+])
+def test_rotation_cache_and_attention_with_one_loud_key(case, dtype, how):
+    """One key is made loud for every query (a score of about 12 against a spread of 1), so a row
+    that sees it copies its value and a row that does not cannot: a window, a kept range or a page
+    that is one position off changes that row entirely. The loud key sits in turn at the start,
+    around the kept range's end, at a page's border, and far back."""
+    c, T = case, 70
+    g = torch.Generator().manual_seed(5)
+    freq, mult = plain.rotary_table("attention" if c["interleaved"] else "attention_2",
+                                    {"base": 100.0, "dims": c["dims"],
+                                     "scaling": ({"factor": 2.0, "original": 16, "fast": 4.0, "slow": 1.0}
+                                                 if c["interleaved"] else {"factor": 2.0})})
+    rd = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
+    for loud in sorted({0, max(c["keep"] - 1, 0), c["keep"], c["page"] - 1, c["page"], 2 * c["page"], 31}):
+        q = 0.3 * torch.randn(T, c["H"], c["Dk"], generator=g)
+        k = 0.3 * torch.randn(T, c["G"], c["Dk"], generator=g)
+        v = torch.randn(T, c["G"], c["Dv"], generator=g) if not c["v_is_k"] else None
+        # the loud direction lies in the columns that are not rotated where there are any (a
+        # rotated pair's score depends on the distance), else everywhere with slow frequencies
+        u = torch.zeros(c["Dk"])
+        u[c["dims"]:] = 1.0
+        if c["dims"] == c["Dk"]:
+            u[:] = 1.0
+        u = u / u.norm()
+        k[loud] += 6.0 * u
+        q += 2.0 * u
+        q, k = q.to(rd).double(), k.to(rd).double()
+        v = v.to(rd).double() if v is not None else None
+        pos = torch.arange(T)
+        mask = plain.visible(T, c["window"], c["keep"])
+        want = plain.sink_softmax_attention(plain.rotate(q, pos, freq, mult, c["interleaved"]),
+                                            plain.rotate(k, pos, freq, mult, c["interleaved"]),
+                                            v if v is not None else k, 1.0, mask)
+        seq = PagedSequence(c["H"], c["G"], c["Dk"], c["Dv"], c["page"], T, dtype, (freq, mult, c["interleaved"]),
+                            c["v_is_k"], seed=loud)
+        cuts = cuts_of(T, how)
+        got = torch.cat([seq.feed(q, k, v, a, b, c["window"], c["keep"], True, 1.0)
+                         for a, b in zip(cuts[:-1], cuts[1:])])
+        assert torch.isfinite(got).all()
+        tol = 2e-5 if dtype == torch.float32 else 3e-2
+        err = (got - want).abs().amax(dim=(1, 2))
+        assert err.max() <= tol * want.abs().max(), (loud, int(err.argmax()), err.max().item())
+        # the test is sharp: moving the window or the kept range by one is far outside the bound
+        for w2, k2 in ((c["window"] + 1, c["keep"]), (c["window"], c["keep"] + 1)):
+            other = plain.sink_softmax_attention(plain.rotate(q, pos, freq, mult, c["interleaved"]),
+                                                 plain.rotate(k, pos, freq, mult, c["interleaved"]),
+                                                 v if v is not None else k, 1.0, plain.visible(T, w2, k2))
+            if not torch.equal(plain.visible(T, w2, k2)[:, loud], mask[:, loud]):
+                assert (other - want).abs().max() > 5 * tol * want.abs().max()
+
+
+@pytest.mark.gpu
+def test_the_sink_shows_where_every_score_is_low():
+    """Queries that point away from every key: without the sink the weights would still sum to
+    one; with it the output shrinks towards zero."""
+    T, D = 12, 8
+    g = torch.Generator().manual_seed(3)
+    k = torch.randn(T, 1, D, generator=g).abs()
+    q = -3.0 * torch.ones(T, 2, D)
+    v = torch.ones(T, 1, D)
+    freq = torch.zeros(0, dtype=torch.float64)
+    seq = PagedSequence(2, 1, D, D, 4, T, torch.float32, (freq, 1.0, False), False)
+    got = seq.feed(q.double(), k.double(), v.double(), 0, T, 50, 0, True, 1.0)
+    want = plain.sink_softmax_attention(q.double(), k.double(), v.double(), 1.0, plain.visible(T, 50))
+    assert (got - want).abs().max() < 1e-6 and got.max() < 0.05
+    seq = PagedSequence(2, 1, D, D, 4, T, torch.float32, (freq, 1.0, False), False)
+    no_sink = seq.feed(q.double(), k.double(), v.double(), 0, T, 50, 0, False, 1.0)
+    assert (no_sink - 1.0).abs().max() < 1e-5
+
+
+# ---------------------------------------------------------------------------------------------
+# the whole model
+# ---------------------------------------------------------------------------------------------
+
+_oracle: dict = {}
+
+
+def oracle(name, folders, reqs):
+    if name not in _oracle:
+        _, w = folders[name]
+        _oracle[name] = {rid: plain.forward(CASES[name]["config"], w, ids)[0] for rid, ids in reqs.items()}
+    return _oracle[name]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_every_way_of_cutting(name, dtype, folders):
+    folder, _ = folders[name]
+    page = CASES[name]["page"]
+    reqs = requests_for(name)
+    want = oracle(name, folders, reqs)
+    results = {}
+    for mode, steps in (("whole", trace_util.whole(reqs)),
+                        ("tail", trace_util.tail_decoded(reqs, 48)),
+                        ("portions", trace_util.portions(reqs)),
+                        ("mixed", trace_util.mixed(reqs, live=4, seed=ord(name)))):
+        # exactly the pages the trace's live requests need at its worst moment, all others and
+        # every page given back full of NaN
+        max_tokens = trace_util.max_live_tokens(steps, page)
+        per_step = trace_util.run_in_process(folder, dtype, steps, max_tokens, page, max_requests=4)
+        got = trace_util.collect(steps, per_step)
+        compare(got, want, (TOL_F32 if dtype == "float32" else TOL_BF16)[name], f"{name} {dtype} {mode}")
+        results[mode] = got
+    for mode in ("tail", "portions", "mixed"):
+        compare(results[mode], results["whole"], (TOL_F32_SAME if dtype == "float32" else TOL_BF16_SAME)[name],
+                f"{name} {dtype} {mode} vs whole")
+
+
+@pytest.mark.gpu
+def test_layer_runs_one_by_one(folders):
+    """The residual stream after every layer run, in 32-bit: a fault shows at the run that has it."""
+    from tokenomos_b200 import models
+    from tokenomos_b200.cache.manager import CacheManager
+    from tokenomos_b200.engine.step import StepEntry, StepFunction
+
+    for name in ("A", "B", "D"):
+        folder, w = folders[name]
+        ids = requests_for(name)["r3"]
+        _, want = plain.forward(CASES[name]["config"], w, ids)
+        conf = models.configure(folder, work="float32")
+        model = models.load(folder, "cuda", conf)
+        cache = CacheManager(model.state_specs(), 8, 40, 2, conf.work, "cuda", max_len=256, poison=True)
+        seen = []
+        for block in model.blocks:
+            def wrapped(h, residual, pending, ctx, call, inner=block.forward):
+                out = inner(h, residual, pending, ctx, call)
+                seen.append((out[1] + out[0]).double().cpu() if out[0] is not None else out[1].double().cpu())
+                return out
+            block.forward = wrapped
+        cache.admit("x")
+        StepFunction(model, cache).run([StepEntry("x", ids, [0])])
+        assert len(seen) == want.shape[0]
+        for run, (got, ref) in enumerate(zip(seen, want)):
+            assert (got - ref).abs().max() <= 2e-5 * ref.abs().max(), (name, run)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(dtype, folders):
+    """One and two token prompts, and 260 tokens decoded one by one: across many pages, far past
+    every window, with the kept first positions many pages behind."""
+    for name in ("B", "D"):
+        folder, w = folders[name]
+        g = torch.Generator().manual_seed(99)
+        vocab = CASES[name]["config"]["vocab"]
+        reqs = {"one": torch.randint(0, vocab, (1,), generator=g).tolist(),
+                "two": torch.randint(0, vocab, (2,), generator=g).tolist(),
+                "long": torch.randint(0, vocab, (263,), generator=g).tolist()}
+        want = {rid: plain.forward(CASES[name]["config"], w, ids)[0] for rid, ids in reqs.items()}
+        steps = trace_util.tail_decoded(reqs, tail=260)
+        page = CASES[name]["page"]
+        per_step = trace_util.run_in_process(folder, dtype, steps, trace_util.max_live_tokens(steps, page), page,
+                                             max_requests=4)
+        compare(trace_util.collect(steps, per_step), want, (TOL_F32 if dtype == "float32" else TOL_BF16)[name],
+                f"long decoding {name} {dtype}")
+
+
+@pytest.mark.gpu
+def test_poisoned_pools_and_a_wrong_window_show(folders, monkeypatch):
+    """Negative controls: the same replay with a window one longer, or without the sink, is far
+    outside the bound that the real model meets."""
+    from tokenomos_b200.parts import attention as att_mod
+
+    name = "B"
+    folder, _ = folders[name]
+    reqs = {k: v for k, v in requests_for(name).items() if k in ("r3", "r4")}
+    want = {rid: oracle(name, folders, requests_for(name))[rid] for rid in reqs}
+    steps = trace_util.portions(reqs)
+    page = CASES[name]["page"]
+    real = att_mod.Attention.__init__
+
+    def run():
+        per_step = trace_util.run_in_process(folder, "float32", steps, trace_util.max_live_tokens(steps, page), page,
+                                             poison=False)
+        return trace_util.collect(steps, per_step)
+
+    compare(run(), want, TOL_F32[name], "control: the real model")
+    for change in ("window", "sink", "keep_first"):
+        def patched(self, *a, **kw):
+            real(self, *a, **kw)
+            if change == "window" and self.window == 16:
+                self.window += 1
+            if change == "sink":
+                self.sink = False
+            if change == "keep_first" and self.keep_first == 20:
+                self.keep_first -= 1
+        monkeypatch.setattr(att_mod.Attention, "__init__", patched)
+        got = run()
+        monkeypatch.setattr(att_mod.Attention, "__init__", real)
+        worst = max(((got[rid] - want[rid]).abs().max() / want[rid].abs().max()).item() for rid in reqs)
+        assert worst > 100 * TOL_F32[name], (change, worst)
+
+
+# ---------------------------------------------------------------------------------------------
+# the entry points: LLM.generate through the scheduler, the command line, the trace program
+# ---------------------------------------------------------------------------------------------
+
+def teacher_forced_ok(config, w, prompt, reply, margin):
+    logits, _ = plain.forward(config, w, prompt + reply)
+    for i, tok in enumerate(reply):
+        row = logits[len(prompt) + i - 1]
+        if int(row.argmax()) != tok:
+            assert row.max().item() - row[tok].item() <= margin, (i, tok, int(row.argmax()))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name, work, graphs", [("A", "fp32", False), ("B", "fp32", True), ("D", "bf16", True),
+                                                ("D", "fp32", False)])
+def test_greedy_generation_through_llm(name, work, graphs, folders):
+    from tokenomos_b200 import LLM, SamplingParams
+
+    folder, w = folders[name]
+    config = CASES[name]["config"]
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, config["vocab"], (n,), generator=g).tolist() for n in (1, 9, 40, 64, 23)]
+    steps = 40
+    with LLM(str(folder), work=work, page=CASES[name]["page"], max_len=256, slots=4, pages=120,
+             prefill_budget=48, poison=True, graphs=graphs) as llm:
+        outs = llm.generate(prompts, SamplingParams(max_tokens=steps))
+    for prompt, out in zip(prompts, outs):
+        assert out.prompt_tokens == len(prompt) and len(out.token_ids) == steps
+        # (measured: every 32-bit token the plain implementation's own argmax; in bfloat16 194 of
+        # 200, the worst 0.08 nats below the best)
+        teacher_forced_ok(config, w, prompt, out.token_ids, 1e-3 if work == "fp32" else 0.2)
+
+
+@pytest.mark.gpu
+def test_trace_program_and_command_line(folders, tmp_path):
+    name = "A"
+    folder, _ = folders[name]
+    reqs = requests_for(name)
+    want = oracle(name, folders, reqs)
+    steps = trace_util.mixed(reqs, live=4, seed=3)
+    per_step = trace_util.run_program(folder, "float32", steps, trace_util.max_live_tokens(steps, 64), tmp_path,
+                                      CASES[name]["config"]["vocab"])
+    compare(trace_util.collect(steps, per_step), want, TOL_F32[name], "trace program")
+    cmd = [sys.executable, "-m", "tokenomos_b200.generate", "--model", str(folder), "--prompt-ids", "1,2,3,4",
+           "--max-tokens", "5", "--arch-kw", '{"work": "fp32"}',
+           "--engine-kw", '{"page": 4, "max_len": 64, "slots": 2, "pages": 40}']
+    proc = subprocess.run(cmd, capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(ln) for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1 and len(lines[0]["token_ids"]) == 5
+    teacher_forced_ok(CASES[name]["config"], folders[name][1], [1, 2, 3, 4], lines[0]["token_ids"], 1e-3)
