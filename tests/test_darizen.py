@@ -83,12 +83,14 @@ CASES = {
 # Bounds relative to the request's largest |logit|, about twice what a B200 measured. Against
 # the float64 plain implementation, 32-bit: A 2.2e-6, B 1.9e-6, C 1.7e-6, D 1.4e-5 (D runs its
 # loud layers three times); bfloat16: A 2.2 %, B 2.3 %, C 3.4 %, D 10 %. Between two ways of
-# cutting the same run, 32-bit: at most 6.7e-6; bfloat16: A 0.18 %, B 0.3 %, C 1e-7, D 1.7 %
-# (a decoded token and a prompt portion round alike but for the attention kernels' tiling).
+# cutting the same run, 32-bit: at most 6.7e-6; bfloat16: A 0.18 %, B 0.3 %, C 1e-7
+# where the general attention kernel runs (a decoded token and a prompt portion round alike but
+# for the order of its sums); D takes the tensor-core kernels, whose prompt and decode forms round
+# the softmax's weights to 16 bits against different running maxima: 4.2 %.
 TOL_F32 = {"A": 1e-5, "B": 1e-5, "C": 1e-5, "D": 4e-5}
 TOL_F32_SAME = {"A": 5e-6, "B": 5e-6, "C": 2e-6, "D": 2e-5}
 TOL_BF16 = {"A": 4.5e-2, "B": 4.5e-2, "C": 6e-2, "D": 0.2}
-TOL_BF16_SAME = {"A": 4e-3, "B": 6e-3, "C": 1e-3, "D": 3.5e-2}
+TOL_BF16_SAME = {"A": 4e-3, "B": 6e-3, "C": 1e-3, "D": 8e-2}
 
 
 def make_tensors(config: dict, seed: int) -> dict[str, torch.Tensor]:
@@ -332,7 +334,7 @@ class PagedSequence:
         self.table = pages.view(1, blocks).cuda()
         self.pool = torch.full((blocks + 5, 2, G, page, max(Dk, Dv)), float("nan"), dtype=dtype, device="cuda")
 
-    def feed(self, q, k, v, a, b, window, keep_first, sink, scale):
+    def feed(self, q, k, v, a, b, window, keep_first, sink, scale, tensor_cores=False, nsplit=1):
         """Positions ``a .. b-1``: rotate, write, attend; returns [b - a, H, Dv]."""
         from tokenomos_b200 import ops
 
@@ -346,6 +348,18 @@ class PagedSequence:
         freq, mult, interleaved = self.rotary
         qr = ops.rotary_write(rows, self.pool, dev(freq), mult, positions, seq, self.table, self.H, self.G,
                               self.Dk, self.Dv, self.P, interleaved, self.v_is_k)
+        if tensor_cores:
+            out = torch.full_like(qr, float("nan"))
+            if n == 1:
+                ops.attention_decode_mma(qr, self.pool, out, positions, seq, self.table, None, window, scale, nsplit,
+                                         None, keep_first, sink)
+            else:
+                per_tile = ops.attention_prefill_mma_tokens(self.H, self.G)
+                tok0 = torch.arange(0, n, per_tile, dtype=torch.int32, device="cuda")
+                ntok = torch.clamp(n - tok0, max=per_tile).to(torch.int32)
+                ops.attention_prefill_mma(qr, self.pool, out, positions, seq, self.table, tok0, ntok, window, scale,
+                                          None, keep_first, sink)
+            return out.cpu().double()
         per_tile = max(1, ops.attention_rows() // (self.H // self.G))
         tok0 = torch.arange(0, n, per_tile, dtype=torch.int32, device="cuda")
         ntok = torch.clamp(n - tok0, max=per_tile).to(torch.int32)
@@ -373,6 +387,10 @@ def cuts_of(T: int, how: str) -> list[int]:
     dict(H=6, G=2, Dk=16, Dv=24, page=8, window=13, keep=3, interleaved=False, v_is_k=False, dims=8),
     dict(H=2, G=2, Dk=24, Dv=8, page=16, window=16, keep=20, interleaved=False, v_is_k=False, dims=12),
     dict(H=3, G=1, Dk=8, Dv=8, page=4, window=1, keep=0, interleaved=True, v_is_k=True, dims=8),
+    # the tensor-core kernels (bfloat16 only): both head sizes, keys over several 64-key tiles
+    dict(H=8, G=2, Dk=64, Dv=64, page=16, window=40, keep=5, interleaved=False, v_is_k=False, dims=32, tc=True),
+    dict(H=4, G=2, Dk=128, Dv=128, page=16, window=24, keep=0, interleaved=True, v_is_k=True, dims=64, tc=True),
+    dict(H=4, G=1, Dk=64, Dv=64, page=8, window=70, keep=66, interleaved=False, v_is_k=False, dims=16, tc=True),
 ])
 def test_rotation_cache_and_attention_with_one_loud_key(case, dtype, how):
     """One key is made loud for every query (a score of about 12 against a spread of 1), so a row
@@ -380,13 +398,19 @@ def test_rotation_cache_and_attention_with_one_loud_key(case, dtype, how):
     that is one position off changes that row entirely. The loud key sits in turn at the start,
     around the kept range's end, at a page's border, and far back."""
     c, T = case, 70
+    tc = bool(c.get("tc"))
+    if tc and dtype != torch.bfloat16:
+        pytest.skip("the tensor-core kernels are bfloat16 kernels")
+    if tc:
+        T = 170
     g = torch.Generator().manual_seed(5)
     freq, mult = plain.rotary_table("attention" if c["interleaved"] else "attention_2",
                                     {"base": 100.0, "dims": c["dims"],
                                      "scaling": ({"factor": 2.0, "original": 16, "fast": 4.0, "slow": 1.0}
                                                  if c["interleaved"] else {"factor": 2.0})})
     rd = torch.bfloat16 if dtype == torch.bfloat16 else torch.float32
-    for loud in sorted({0, max(c["keep"] - 1, 0), c["keep"], c["page"] - 1, c["page"], 2 * c["page"], 31}):
+    for loud in sorted({0, max(c["keep"] - 1, 0), c["keep"], c["page"] - 1, c["page"], 2 * c["page"], 31}
+                       | ({63, 64, 100} if tc else set())):
         q = 0.3 * torch.randn(T, c["H"], c["Dk"], generator=g)
         k = 0.3 * torch.randn(T, c["G"], c["Dk"], generator=g)
         v = torch.randn(T, c["G"], c["Dv"], generator=g) if not c["v_is_k"] else None
@@ -409,7 +433,7 @@ def test_rotation_cache_and_attention_with_one_loud_key(case, dtype, how):
         seq = PagedSequence(c["H"], c["G"], c["Dk"], c["Dv"], c["page"], T, dtype, (freq, mult, c["interleaved"]),
                             c["v_is_k"], seed=loud)
         cuts = cuts_of(T, how)
-        got = torch.cat([seq.feed(q, k, v, a, b, c["window"], c["keep"], True, 1.0)
+        got = torch.cat([seq.feed(q, k, v, a, b, c["window"], c["keep"], True, 1.0, tc, 1 + (a % 3))
                          for a, b in zip(cuts[:-1], cuts[1:])])
         assert torch.isfinite(got).all()
         tol = 2e-5 if dtype == torch.float32 else 3e-2

@@ -61,13 +61,30 @@ __device__ __forceinline__ float head_gate_of(const __nv_bfloat16* gate, int64_t
     return round_as<__nv_bfloat16>(1.0f / (1.0f + expf(-g)));
 }
 
+// Options of a layer's attention beyond window and scale. `keep_first`: with a window, keys at
+// positions below it stay visible to every later query. `sink`: the softmax's denominator has one
+// more term, a key of score 0 that has no value (every row's running maximum and sum start from
+// it). `gate_mode`: 0 none, 1 one gate per (token, head), 2 one per output element ([T, H * D]
+// rows `ldg` apart; the 32-bit output times the 32-bit sigmoid is rounded once).
+struct AttnOptions {
+    int keep_first;
+    int sink;
+    int gate_mode;
+};
+
+__device__ __forceinline__ float elem_gate_of(const __nv_bfloat16* gate, int64_t ldg, int tok, int col) {
+    const float g = __bfloat162float(gate[(size_t)tok * ldg + col]);
+    return 1.0f / (1.0f + expf(-g));
+}
+
 // One 16-row x NK-key block of the online softmax for a warp: S = Q K^T from `ktile`, mask,
 // update (m, l, O) with V from `vtile`. NK is 64 (prefill) or 32 (decode).
 template <int D, int NK>
 __device__ __forceinline__ void warp_block(const uint32_t (&qf)[D / 16][4], uint32_t ktile,
                                            uint32_t vtile, int j0, int pos_lo, int pos_hi,
                                            int window, float scale_log2, bool need_mask,
-                                           float (&m)[2], float (&l)[2], float (&o)[D / 8][4]) {
+                                           float (&m)[2], float (&l)[2], float (&o)[D / 8][4],
+                                           int keep_first = 0, int j_lo = -0x7fffffff, int j_hi = 0x7fffffff) {
     const int lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     float s[NK / 8][4];
@@ -98,7 +115,8 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[D / 16][4], uint
             for (int e = 0; e < 4; ++e) {
                 const int j = j0 + n * 8 + 2 * t + (e & 1);
                 const int pos = (e < 2) ? pos_lo : pos_hi;
-                const bool visible = j <= pos && (window <= 0 || pos - j < window);
+                const bool visible = j <= pos && (window <= 0 || pos - j < window || j < keep_first) &&
+                                     j >= j_lo && j <= j_hi;
                 if (!visible) s[n][e] = -INFINITY;
             }
         }
@@ -190,14 +208,16 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[D / 16][4], const __nv_bfl
 // ---------------------------------------------------------------------------------------------
 // prefill: 64 rows per CTA, all keys
 // ---------------------------------------------------------------------------------------------
-template <int D>
+// X: whether the options of AttnOptions are compiled in (the plain kernel is the X = false one)
+template <int D, bool X = false>
 __global__ void __launch_bounds__(128, (D == 64 ? 4 : 2))
 attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                         __nv_bfloat16* out, const int* positions,
                         const int* tok_seq, const int* block_table,
                         int bt_stride, const int* tile_tok0,
                         const int* tile_ntok, int H, int Hkv, int P, int window,
-                        float scale, int p_shift, const __nv_bfloat16* gate, int64_t ldg) {
+                        float scale, int p_shift, const __nv_bfloat16* gate, int64_t ldg,
+                        const AttnOptions opt) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -231,7 +251,13 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
     const int w_pos_max = w_last_row >= warp * 16 ? pos_first + w_last_row / G : -1;
     const int w_pos_min = pos_first + (warp * 16) / G;
 
+    // (a sink is a key of score 0 without a value: the running maximum and sum start from it;
+    // the sum is kept in four parts, one per thread of a row)
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (X && opt.sink) {
+        m[0] = m[1] = 0.f;
+        l[0] = l[1] = (lane & 3) == 0 ? 1.f : 0.f;
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int n = 0; n < D / 8; ++n)
@@ -239,36 +265,63 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         for (int e = 0; e < 4; ++e) o[n][e] = 0.f;
     const float scale_log2 = scale * LOG2E;
 
-    const int n_tiles = (pos_last - j_begin) / 64 + 1;
+    // the key tiles: first those of the kept positions that lie before the window of the tile's
+    // first row, [0, keep_end), then from the window's start to the last row's position
+    const int keep_first = X ? opt.keep_first : 0;
+    const int keep_end = (keep_first > 0 && lo > 0) ? min(keep_first, lo) : 0;
+    const int n_keep = (keep_end + 63) / 64;
+    const int n_tiles = n_keep + (pos_last - j_begin) / 64 + 1;
+    auto range = [&](int it, int& j0, int& j_lo, int& j_hi) {
+        if (it < n_keep) {
+            j0 = it * 64, j_lo = 0, j_hi = keep_end - 1;
+        } else {
+            j0 = j_begin + (it - n_keep) * 64, j_lo = lo, j_hi = pos_last;
+        }
+    };
     PagedLoader<D, 64, 128> loader;
     loader.init(tid, kvh, Hkv, P, p_shift);
     auto issue = [&](int it) {
         const uint32_t base = smem + (uint32_t)(it & 1) * 2 * TILE_BYTES;
-        const int j0 = j_begin + it * 64;
+        int j0, j_lo, j_hi;
+        range(it, j0, j_lo, j_hi);
         if (p_shift >= 0) {
             // (pages looked up one tile ahead, as in the decode kernel)
-            loader.issue_looked_up(base, base + TILE_BYTES, pool, j0, lo, pos_last);
-            if (it + 1 < n_tiles) loader.lookup(bt_row, j0 + 64, lo, pos_last);
+            loader.issue_looked_up(base, base + TILE_BYTES, pool, j0, j_lo, j_hi);
+            if (it + 1 < n_tiles) {
+                range(it + 1, j0, j_lo, j_hi);
+                loader.lookup(bt_row, j0, j_lo, j_hi);
+            }
         } else {
-            load_tile<D>(base, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
-            load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 64, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
+            load_tile<D>(base, pool, bt_row, j0, 64, j_lo, j_hi, kvh, Hkv, P, 0, tid, 128);
+            load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 64, j_lo, j_hi, kvh, Hkv, P, 1, tid, 128);
         }
         cp_async_commit();
     };
-    if (p_shift >= 0) loader.lookup(bt_row, j_begin, lo, pos_last);
+    if (p_shift >= 0) {
+        int j0, j_lo, j_hi;
+        range(0, j0, j_lo, j_hi);
+        loader.lookup(bt_row, j0, j_lo, j_hi);
+    }
     issue(0);
     for (int it = 0; it < n_tiles; ++it) {
         cp_async_wait<0>();
         __syncthreads();
         if (it + 1 < n_tiles) issue(it + 1);
-        const int j0 = j_begin + it * 64;
-        const bool active = w_pos_max >= j0 && (window <= 0 || j0 + 63 > w_pos_min - window);
+        int j0, j_lo, j_hi;
+        range(it, j0, j_lo, j_hi);
+        const bool kept = it < n_keep;
+        const bool active = kept ? w_pos_max >= 0
+                                 : w_pos_max >= j0 && (window <= 0 || j0 + 63 > w_pos_min - window || j0 < keep_first);
         if (active) {
-            const bool need_mask = (j0 + 63 > w_pos_min) || (window > 0 && j0 <= w_pos_max - window) ||
+            const bool need_mask = kept || (j0 + 63 > w_pos_min) || (window > 0 && j0 <= w_pos_max - window) ||
                                    pos_lo < 0 || pos_hi < 0;
             const uint32_t base = smem + (uint32_t)(it & 1) * 2 * TILE_BYTES;
-            warp_block<D, 64>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2,
-                              need_mask, m, l, o);
+            if (keep_first > 0)
+                warp_block<D, 64>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2,
+                                  need_mask, m, l, o, keep_first, j_lo, j_hi);
+            else
+                warp_block<D, 64>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2,
+                                  need_mask, m, l, o);
         }
     }
     // finish: row sums over the 4 threads of a row, normalise, store
@@ -284,9 +337,17 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         if (r >= rows) continue;
         const float inv = l[half] > 0.f ? 1.0f / l[half] : 0.f;
         __nv_bfloat16* dst = out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * D;
-        const float gs = head_gate_of(gate, ldg, tok0 + r / G, kvh * G + r % G);
+        const bool by_element = X && opt.gate_mode == 2;
+        const float gs = by_element ? 1.0f : head_gate_of(gate, ldg, tok0 + r / G, kvh * G + r % G);
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
+            if (by_element) {
+                const int col = (kvh * G + r % G) * D + n * 8 + 2 * t;
+                *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) =
+                    pack_bf16(o[n][half * 2] * inv * elem_gate_of(gate, ldg, tok0 + r / G, col),
+                              o[n][half * 2 + 1] * inv * elem_gate_of(gate, ldg, tok0 + r / G, col + 1));
+                continue;
+            }
             uint32_t v = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
             if (gate != nullptr) {
                 const float2 f = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
@@ -300,14 +361,15 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
 // ---------------------------------------------------------------------------------------------
 // decode: one token per sequence; CTA (token, kv head, split); warps take alternate 32-key tiles
 // ---------------------------------------------------------------------------------------------
-template <int D>
+template <int D, bool X = false>
 __global__ void __launch_bounds__(128)
 attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
                        __nv_bfloat16* out, const int* positions,
                        const int* tok_seq, const int* block_table,
                        int bt_stride, const int* tok_index, int H, int Hkv, int P,
                        int window, float scale, int nsplit, float* part_o,
-                       float* part_ml, int p_shift, const __nv_bfloat16* gate, int64_t ldg) {
+                       float* part_ml, int p_shift, const __nv_bfloat16* gate, int64_t ldg,
+                       const AttnOptions opt) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -324,14 +386,30 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
     const int g = lane >> 2, t = lane & 3;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int j_begin = (lo / 32) * 32;
-    const int tiles = (pos - j_begin) / 32 + 1;
+    // the key tiles: first those of the kept positions before the window, [0, keep_end), then
+    // from the window's start to the token's own position
+    const int keep_first = X ? opt.keep_first : 0;
+    const int keep_end = (keep_first > 0 && lo > 0) ? min(keep_first, lo) : 0;
+    const int n_keep = (keep_end + 31) / 32;
+    const int tiles = n_keep + (pos - j_begin) / 32 + 1;
     const int per_split = (tiles + nsplit - 1) / nsplit;
     const int t_begin = split * per_split, t_end = min(tiles, t_begin + per_split);
+    auto range = [&](int tile, int& j0, int& j_lo, int& j_hi) {
+        if (tile < n_keep) {
+            j0 = tile * 32, j_lo = 0, j_hi = keep_end - 1;
+        } else {
+            j0 = j_begin + (tile - n_keep) * 32, j_lo = lo, j_hi = pos;
+        }
+    };
 
     uint32_t qf[D / 16][4];
     load_q<D>(qf, q, 0, G, tok, G, H, kvh * G);      // rows 0..G-1 are the group's heads
     const int pos_lo = g < G ? pos : -1, pos_hi = g + 8 < G ? pos : -1;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (X && opt.sink && split == 0 && warp == 0) {       // the sink joins one warp's share, once
+        m[0] = m[1] = 0.f;
+        l[0] = l[1] = t == 0 ? 1.f : 0.f;
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int n = 0; n < D / 8; ++n)
@@ -345,21 +423,29 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
     loader.init(lane, kvh, Hkv, P, p_shift);
     auto issue = [&](int tile, int stage) {
         const uint32_t base = wbase + (uint32_t)stage * 2 * TILE_BYTES;
-        const int j0 = j_begin + tile * 32;
+        int j0, j_lo, j_hi;
+        range(tile, j0, j_lo, j_hi);
         if (p_shift >= 0) {
             // the pages of this tile were looked up when the tile before it was issued; now the
             // next tile's are, so that no copy waits for a block-table entry
-            loader.issue_looked_up(base, base + TILE_BYTES, pool, j0, lo, pos);
-            if (tile + 4 < t_end) loader.lookup(bt_row, j0 + 4 * 32, lo, pos);
+            loader.issue_looked_up(base, base + TILE_BYTES, pool, j0, j_lo, j_hi);
+            if (tile + 4 < t_end) {
+                range(tile + 4, j0, j_lo, j_hi);
+                loader.lookup(bt_row, j0, j_lo, j_hi);
+            }
         } else {
-            load_tile<D>(base, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 0, lane, 32);
-            load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 32, lo, pos, kvh, Hkv, P, 1, lane, 32);
+            load_tile<D>(base, pool, bt_row, j0, 32, j_lo, j_hi, kvh, Hkv, P, 0, lane, 32);
+            load_tile<D>(base + TILE_BYTES, pool, bt_row, j0, 32, j_lo, j_hi, kvh, Hkv, P, 1, lane, 32);
         }
         cp_async_commit();
     };
     int stage = 0;
     if (t_begin + warp < t_end) {
-        if (p_shift >= 0) loader.lookup(bt_row, j_begin + (t_begin + warp) * 32, lo, pos);
+        if (p_shift >= 0) {
+            int j0, j_lo, j_hi;
+            range(t_begin + warp, j0, j_lo, j_hi);
+            loader.lookup(bt_row, j0, j_lo, j_hi);
+        }
         issue(t_begin + warp, 0);
     }
     for (int tile = t_begin + warp; tile < t_end; tile += 4) {
@@ -367,11 +453,16 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         if (more) issue(tile + 4, stage ^ 1);
         if (more) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncwarp();
-        const int j0 = j_begin + tile * 32;
+        int j0, j_lo, j_hi;
+        range(tile, j0, j_lo, j_hi);
         const bool need_mask = true;                 // rows past G are always masked
         const uint32_t base = wbase + (uint32_t)stage * 2 * TILE_BYTES;
-        warp_block<D, 32>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2,
-                          need_mask, m, l, o);
+        if (keep_first > 0)
+            warp_block<D, 32>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2,
+                              need_mask, m, l, o, keep_first, j_lo, j_hi);
+        else
+            warp_block<D, 32>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2,
+                              need_mask, m, l, o);
         __syncwarp();
         stage ^= 1;
     }
@@ -412,7 +503,10 @@ attn_decode_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
             acc += sm_o[(w * 16 + r) * D + c] * f;
         }
         const int head = kvh * G + r;
-        if (nsplit == 1) {
+        if (X && nsplit == 1 && opt.gate_mode == 2) {
+            out[((size_t)tok * H + head) * D + c] =
+                __float2bfloat16_rn((L > 0.f ? acc / L : 0.f) * elem_gate_of(gate, ldg, tok, head * D + c));
+        } else if (nsplit == 1) {
             float y = round_as<__nv_bfloat16>(L > 0.f ? acc / L : 0.f);
             if (gate != nullptr) y *= head_gate_of(gate, ldg, tok, head);
             out[((size_t)tok * H + head) * D + c] = __float2bfloat16_rn(y);
@@ -432,7 +526,7 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
                                          const float* part_ml,
                                          __nv_bfloat16* out,
                                          const int* tok_index, int H, int nsplit,
-                                         float scale, const __nv_bfloat16* gate, int64_t ldg) {
+                                         float scale, const __nv_bfloat16* gate, int64_t ldg, int gate_mode) {
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x, head = blockIdx.y, c = threadIdx.x;
@@ -448,6 +542,11 @@ __global__ void attn_decode_merge_kernel(const float* part_o,
         const float f = ms == -INFINITY ? 0.f : fast_exp2((ms - M) * scale_log2);
         L += part_ml[(base + s) * 2 + 1] * f;
         acc += part_o[(base + s) * D + c] * f;
+    }
+    if (gate_mode == 2) {
+        out[((size_t)tok * H + head) * D + c] =
+            __float2bfloat16_rn((L > 0.f ? acc / L : 0.f) * elem_gate_of(gate, ldg, tok, head * D + c));
+        return;
     }
     float y = round_as<__nv_bfloat16>(L > 0.f ? acc / L : 0.f);
     if (gate != nullptr) y *= head_gate_of(gate, ldg, tok, head);
@@ -832,11 +931,17 @@ TK_API int tk_attn_mma_supported(int H, int Hkv, int D) { return mma_shape_ok(H,
 // Tokens per tile the prefill kernel expects: 64 rows / G heads.
 TK_API int tk_attn_prefill_mma_tokens(int H, int Hkv) { return 64 / (H / Hkv); }
 
-TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, const int* positions,
-                               const int* tok_seq, const int* block_table, int bt_stride,
-                               const int* tile_tok0, const int* tile_ntok, int n_tiles, int H,
-                               int Hkv, int D, int P, int window, float scale, const void* gate,
-                               int64_t ldg, cudaStream_t stream) {
+// `keep_first`, `sink`, `gate_mode`: see AttnOptions (all zero: plain windowed attention with a
+// per-head gate when `gate` is given).
+TK_API int tk_attn_prefill_mma_opt(const void* q, const void* kv_pool, void* out, const int* positions,
+                                   const int* tok_seq, const int* block_table, int bt_stride,
+                                   const int* tile_tok0, const int* tile_ntok, int n_tiles, int H,
+                                   int Hkv, int D, int P, int window, float scale, const void* gate,
+                                   int64_t ldg, int keep_first, int sink, int gate_mode, cudaStream_t stream) {
+    TK_CHECK_ARG(keep_first >= 0 && (keep_first == 0 || window > 0), "attn_prefill_mma: kept first positions need a window");
+    TK_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0) == (gate == nullptr),
+                 "attn_prefill_mma: gate mode %d and the gate do not go together", gate_mode);
+    const AttnOptions opt{keep_first, sink ? 1 : 0, gate_mode};
     TK_CHECK_ARG(mma_shape_ok(H, Hkv, D), "attn_prefill_mma: shape H=%d Hkv=%d D=%d is not taken "
                  "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attn_prefill_mma: bad page size or tile count");
@@ -847,17 +952,36 @@ TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, co
     auto p_ = (const __nv_bfloat16*)kv_pool;
     auto o_ = (__nv_bfloat16*)out;
     auto g_ = (const __nv_bfloat16*)gate;
-    if (D == 64) {
+    const bool x = keep_first > 0 || sink || gate_mode == 2;
+    if (x && D == 64) {
+        cudaFuncSetAttribute(attn_prefill_mma_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_prefill_mma_kernel<64, true>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq,
+                  block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P), g_, ldg, opt);
+    } else if (x) {
+        cudaFuncSetAttribute(attn_prefill_mma_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_prefill_mma_kernel<128, true>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq,
+                  block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P), g_, ldg, opt);
+    } else if (D == 64) {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_prefill_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table,
-                                                                 bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P), g_, ldg);
+                                                                 bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P), g_, ldg, opt);
     } else {
         cudaFuncSetAttribute(attn_prefill_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_prefill_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table,
-                                                                  bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P), g_, ldg);
+                                                                  bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, page_shift(P), g_, ldg, opt);
     }
     TK_CHECK_LAUNCH("attn_prefill_mma");
     return 0;
+}
+
+TK_API int tk_attn_prefill_mma(const void* q, const void* kv_pool, void* out, const int* positions,
+                               const int* tok_seq, const int* block_table, int bt_stride,
+                               const int* tile_tok0, const int* tile_ntok, int n_tiles, int H,
+                               int Hkv, int D, int P, int window, float scale, const void* gate,
+                               int64_t ldg, cudaStream_t stream) {
+    return tk_attn_prefill_mma_opt(q, kv_pool, out, positions, tok_seq, block_table, bt_stride, tile_tok0, tile_ntok,
+                                   n_tiles, H, Hkv, D, P, window, scale, gate, ldg, 0, 0, gate != nullptr ? 1 : 0,
+                                   stream);
 }
 
 // Floats of scratch the decode kernel needs for `n` tokens split `nsplit` ways:
@@ -866,11 +990,15 @@ TK_API int64_t tk_attn_decode_mma_scratch(int n, int H, int D, int nsplit) {
     return nsplit <= 1 ? 0 : (int64_t)n * H * nsplit * (D + 2);
 }
 
-TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, const int* positions,
-                              const int* tok_seq, const int* block_table, int bt_stride,
-                              const int* tok_index, int n, int H, int Hkv, int D, int P, int window,
-                              float scale, int nsplit, float* scratch, const void* gate, int64_t ldg,
-                              cudaStream_t stream) {
+TK_API int tk_attn_decode_mma_opt(const void* q, const void* kv_pool, void* out, const int* positions,
+                                  const int* tok_seq, const int* block_table, int bt_stride,
+                                  const int* tok_index, int n, int H, int Hkv, int D, int P, int window,
+                                  float scale, int nsplit, float* scratch, const void* gate, int64_t ldg,
+                                  int keep_first, int sink, int gate_mode, cudaStream_t stream) {
+    TK_CHECK_ARG(keep_first >= 0 && (keep_first == 0 || window > 0), "attn_decode_mma: kept first positions need a window");
+    TK_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0) == (gate == nullptr),
+                 "attn_decode_mma: gate mode %d and the gate do not go together", gate_mode);
+    const AttnOptions opt{keep_first, sink ? 1 : 0, gate_mode};
     TK_CHECK_ARG(mma_shape_ok(H, Hkv, D), "attn_decode_mma: shape H=%d Hkv=%d D=%d is not taken "
                  "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n >= 0 && nsplit >= 1 && nsplit <= 65535, "attn_decode_mma: bad sizes");
@@ -887,23 +1015,52 @@ TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, con
     auto p_ = (const __nv_bfloat16*)kv_pool;
     auto o_ = (__nv_bfloat16*)out;
     auto g_ = (const __nv_bfloat16*)gate;
-    if (D == 64) {
-        cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        tk_launch(attn_decode_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
-                                                                tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P), g_, ldg);
+    const bool x = keep_first > 0 || sink || gate_mode == 2;
+    if (x && D == 64) {
+        cudaFuncSetAttribute(attn_decode_mma_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_mma_kernel<64, true>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq,
+                  block_table, bt_stride, tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P),
+                  g_, ldg, opt);
         TK_CHECK_LAUNCH("attn_decode_mma");
         if (nsplit > 1)
-            tk_launch(attn_decode_merge_kernel<64>, dim3(dim3(n, H)), dim3(64), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale, g_, ldg);
+            tk_launch(attn_decode_merge_kernel<64>, dim3(dim3(n, H)), dim3(64), 0, stream, part_o, part_ml, o_, tok_index,
+                      H, nsplit, scale, g_, ldg, gate_mode);
+    } else if (x) {
+        cudaFuncSetAttribute(attn_decode_mma_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_mma_kernel<128, true>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq,
+                  block_table, bt_stride, tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P),
+                  g_, ldg, opt);
+        TK_CHECK_LAUNCH("attn_decode_mma");
+        if (nsplit > 1)
+            tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_,
+                      tok_index, H, nsplit, scale, g_, ldg, gate_mode);
+    } else if (D == 64) {
+        cudaFuncSetAttribute(attn_decode_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_mma_kernel<64>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
+                                                                tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P), g_, ldg, opt);
+        TK_CHECK_LAUNCH("attn_decode_mma");
+        if (nsplit > 1)
+            tk_launch(attn_decode_merge_kernel<64>, dim3(dim3(n, H)), dim3(64), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale, g_, ldg, gate_mode);
     } else {
         cudaFuncSetAttribute(attn_decode_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_decode_mma_kernel<128>, dim3(grid), dim3(128), smem, stream, q_, p_, o_, positions, tok_seq, block_table, bt_stride,
-                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P), g_, ldg);
+                                                                 tok_index, H, Hkv, P, window, scale, nsplit, part_o, part_ml, page_shift(P), g_, ldg, opt);
         TK_CHECK_LAUNCH("attn_decode_mma");
         if (nsplit > 1)
-            tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale, g_, ldg);
+            tk_launch(attn_decode_merge_kernel<128>, dim3(dim3(n, H)), dim3(128), 0, stream, part_o, part_ml, o_, tok_index, H, nsplit, scale, g_, ldg, gate_mode);
     }
     TK_CHECK_LAUNCH("attn_decode_merge");
     return 0;
+}
+
+TK_API int tk_attn_decode_mma(const void* q, const void* kv_pool, void* out, const int* positions,
+                              const int* tok_seq, const int* block_table, int bt_stride,
+                              const int* tok_index, int n, int H, int Hkv, int D, int P, int window,
+                              float scale, int nsplit, float* scratch, const void* gate, int64_t ldg,
+                              cudaStream_t stream) {
+    return tk_attn_decode_mma_opt(q, kv_pool, out, positions, tok_seq, block_table, bt_stride, tok_index, n, H, Hkv,
+                                  D, P, window, scale, nsplit, scratch, gate, ldg, 0, 0, gate != nullptr ? 1 : 0,
+                                  stream);
 }
 
 // 1 when tk_attn_decode_fused takes this shape: what the tensor-core kernels take, and a rotation

@@ -394,31 +394,42 @@ def _check_attention(q, kv_pool, name):
 
 
 def _gate_view(gate: torch.Tensor | None, T: int, H: int, name: str):
-    """(pointer, row stride) of a per-head output gate [T, H] (a bfloat16 view with unit column
-    stride), or (None, 0)."""
+    """(pointer, row stride) of an output gate [T, H] (one per head; with ``H`` the row's whole
+    width, one per element: a bfloat16 view with unit column stride), or (None, 0)."""
     if gate is None:
         return None, 0
     if not gate.is_cuda or gate.dtype != torch.bfloat16 or tuple(gate.shape) != (T, H) or gate.stride(1) != 1:
-        raise KernelError(f"{name}: gate must be a bfloat16 [T, H] CUDA view with unit column stride")
+        raise KernelError(f"{name}: gate must be a bfloat16 [T, {H}] CUDA view with unit column stride")
     return gate.data_ptr(), gate.stride(0)
+
+
+def _gate_options(gate, gate_by_element: bool, T: int, H: int, D: int, name: str):
+    """(pointer, row stride, gate mode of the kernels: 0 none, 1 per head, 2 per element)."""
+    if gate is None:
+        return None, 0, 0
+    g_ptr, ldg = _gate_view(gate, T, H * D if gate_by_element else H, name)
+    return g_ptr, ldg, 2 if gate_by_element else 1
 
 
 def attention_prefill_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
                           positions: torch.Tensor, tok_seq: torch.Tensor,
                           block_table: torch.Tensor, tile_tok0: torch.Tensor,
                           tile_ntok: torch.Tensor, window: int | None, scale: float,
-                          gate: torch.Tensor | None = None) -> None:
+                          gate: torch.Tensor | None = None, keep_first: int = 0, sink: bool = False,
+                          gate_by_element: bool = False) -> None:
     """Tensor-core attention for tiles of ``attention_prefill_mma_tokens`` tokens of one
     sequence; writes the tiles' rows of ``out`` [T, H, D], times the per-head output gate
-    ``round(sigmoid(gate))`` [T, H] if one is given."""
+    ``round(sigmoid(gate))`` [T, H] if one is given. ``keep_first``, ``sink``: as in
+    ``attention``; ``gate_by_element``: ``gate`` is [T, H * D], one value per output element, and
+    the 32-bit output times the 32-bit sigmoid is rounded once."""
     _cuda(q, kv_pool, out, positions, tok_seq, block_table, tile_tok0, tile_ntok)
     T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_prefill_mma")
-    g_ptr, ldg = _gate_view(gate, T, H, "attention_prefill_mma")
-    _lib.call("tk_attn_prefill_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
+    g_ptr, ldg, mode = _gate_options(gate, gate_by_element, T, H, D, "attention_prefill_mma")
+    _lib.call("tk_attn_prefill_mma_opt", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
               block_table.stride(0), _ptr(_i32(tile_tok0, "tile_tok0")),
               _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(), H, Hkv, D, P, int(window or 0),
-              float(scale), g_ptr, ldg, _stream())
+              float(scale), g_ptr, ldg, int(keep_first), int(bool(sink)), mode, _stream())
 
 
 def attention_prefill_tc_supported(heads: int, kv_heads: int, head_dim: int, dtype: torch.dtype) -> bool:
@@ -465,7 +476,8 @@ def attention_prefill_tc_status() -> int:
 def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tensor,
                          positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
                          tok_index: torch.Tensor | None, window: int | None, scale: float,
-                         nsplit: int, gate: torch.Tensor | None = None) -> None:
+                         nsplit: int, gate: torch.Tensor | None = None, keep_first: int = 0,
+                         sink: bool = False, gate_by_element: bool = False) -> None:
     """Tensor-core attention for sequences that bring one token (``tok_index``: their rows in
     the packed batch; None: every row of ``q`` is one, in order, which spares the kernel a
     lookup), each split ``nsplit`` ways over its keys; partial results go through scratch memory
@@ -473,16 +485,16 @@ def attention_decode_mma(q: torch.Tensor, kv_pool: torch.Tensor, out: torch.Tens
     (gated like ``attention_prefill_mma``'s)."""
     _cuda(q, kv_pool, out, positions, tok_seq, block_table, tok_index)
     T, H, D, Hkv, P = _check_attention(q, kv_pool, "attention_decode_mma")
-    g_ptr, ldg = _gate_view(gate, T, H, "attention_decode_mma")
+    g_ptr, ldg, mode = _gate_options(gate, gate_by_element, T, H, D, "attention_decode_mma")
     n = tok_index.numel() if tok_index is not None else T
     scratch = None
     if nsplit > 1:
         scratch = torch.empty(n * H * nsplit * (D + 2), dtype=torch.float32, device=q.device)
-    _lib.call("tk_attn_decode_mma", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
+    _lib.call("tk_attn_decode_mma_opt", _ptr(q), _ptr(kv_pool), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")),
               block_table.stride(0), _ptr(_i32(tok_index, "tok_index") if tok_index is not None else None),
               n, H, Hkv, D, P, int(window or 0), float(scale), int(nsplit), _ptr(scratch), g_ptr, ldg,
-              _stream())
+              int(keep_first), int(bool(sink)), mode, _stream())
 
 
 def attention_decode_fused_supported(heads: int, kv_heads: int, head_dim: int, rotary: int,

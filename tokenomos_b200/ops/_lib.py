@@ -43,6 +43,8 @@ _SIGNATURES = {
     "tk_attn_mma_supported": [I, I, I],
     "tk_attn_prefill_mma_tokens": [I, I],
     "tk_attn_prefill_mma": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, L, P],
+    "tk_attn_prefill_mma_opt": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, F, P, L, I, I, I, P],
+    "tk_attn_decode_mma_opt": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P, L, I, I, I, P],
     "tk_attn_prefill_tc_supported": [I, I, I],
     "tk_attn_prefill_tc_tokens": [I, I],
     "tk_attn_prefill_tc_status": [],

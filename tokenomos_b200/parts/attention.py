@@ -51,7 +51,9 @@ class Attention:
                              f"{ops.ATTENTION_MAX_HEAD_DIM} the attention kernels take")
         self.sink, self.keep_first, self.v_dim, self.v_is_k = bool(sink), int(keep_first), v_dim, bool(v_is_k)
         self.gate_kind, self.exact = gate_kind, bool(exact)
-        # what only the general kernels compute (the fused and tensor-core forms take none of it)
+        # what the one-kernel decode form, the tcgen05 prefill kernel and the norms folded into
+        # the projections do not take (the mma.sync kernels take all of it but a value size of
+        # its own; the general kernel takes everything)
         self.extended = bool(self.sink or self.keep_first or self.v_is_k or v_dim != head_dim
                              or gate_kind != "head" or self.exact)
         if heads % kv_heads:
@@ -174,7 +176,9 @@ class Attention:
         own_kv = self.head_layout.kv_heads
         q = self.rope.encode_qk(qkv, ctx, self.head_layout, pool if own_kv else None,
                                 table if own_kv else None)
-        if not self.extended and ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim, q.dtype):
+        # the tensor-core kernels take everything but value heads of another size than the keys
+        if self.v_dim == self.head_dim and ops.attention_mma_supported(self.heads, self.kv_heads, self.head_dim,
+                                                                       q.dtype):
             return self._attend_mma(q, pool, table, ctx, gate)
         rows = ops.attention_rows()
         group = self.heads // self.kv_heads
@@ -238,8 +242,11 @@ class Attention:
         out = torch.empty_like(q)
         # prompt portions: the tcgen05 kernel (tiles of 128 rows) where it takes the shape, else
         # the mma.sync one (tiles of 64 rows)
-        tc = self.prefill_tc and ops.attention_prefill_tc_supported(self.heads, self.kv_heads, self.head_dim,
-                                                                     q.dtype)
+        # (the tcgen05 kernel is the plain form's: a sink, kept positions or a gate per element
+        # go to the mma.sync kernel)
+        tc = (self.prefill_tc and not (self.sink or self.keep_first or self.gate_kind != "head")
+              and ops.attention_prefill_tc_supported(self.heads, self.kv_heads, self.head_dim, q.dtype))
+        by_element = self.gate_kind == "element"
         per_tile = (ops.attention_prefill_tc_tokens if tc else ops.attention_prefill_mma_tokens)(
             self.heads, self.kv_heads)
         _, tok0, _, ntok = ctx.tiles(per_tile, "multi")
@@ -249,7 +256,7 @@ class Attention:
                                      self.scale, gate, nsplit)
         elif tok0.numel():
             ops.attention_prefill_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window,
-                                      self.scale, gate)
+                                      self.scale, gate, self.keep_first, self.sink, by_element)
         # every sequence brings one token: row i is sequence i's, no list of rows needed
         decode_only = ctx.host.decode_only
         singles = None if decode_only else ctx.singles()
@@ -260,7 +267,7 @@ class Attention:
             rows = ctx.n_tokens if decode_only else singles.numel()
             nsplit = self.decode_splits(rows, self.kv_heads, longest, self.tuning)
             ops.attention_decode_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, singles,
-                                     self.window, self.scale, nsplit, gate)
+                                     self.window, self.scale, nsplit, gate, self.keep_first, self.sink, by_element)
         return out
 
 
