@@ -881,6 +881,206 @@ def prefill_flops(config: dict, tokens: int) -> float:
     return flops + 2 * config["vocab_size"] * d
 
 
+# ---------------------------------------------------------------------------------------------
+# --design darizen: the Darizen decoder beside the closest LFM3 configuration at equal sizes
+# ---------------------------------------------------------------------------------------------
+DESIGN_SIZES = {
+    # name: width, heads, kv heads, head size, feed-forward, layers, vocabulary, window
+    "w2048_d64": dict(width=2048, heads=32, kv_heads=8, dim=64, ff=8192, layers=8, vocab=65536, window=1024),
+    "w1024_d64": dict(width=1024, heads=16, kv_heads=4, dim=64, ff=4608, layers=8, vocab=65536, window=1024),
+    "w2048_d128": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, layers=8, vocab=65536, window=1024),
+}
+
+
+def darizen_config(z: dict) -> dict:
+    """Layers alternate between the two mixers; every layer has a feed-forward; no loop (the
+    LFM3 stack beside it has none)."""
+    layers = []
+    for i in range(z["layers"]):
+        second = i % 2 == 0
+        mixer = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"],
+                 "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]},
+                 "rot": {"base": 1000000.0, "dims": z["dim"]}}
+        if second:
+            mixer["mask"]["keep_first"] = 4
+            mixer["rot"]["scaling"] = {"factor": 8.0}
+        else:
+            mixer["rot"]["scaling"] = {"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0}
+        layers.append({"type": "attention_2" if second else "attention", "mixer": mixer,
+                       "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0}})
+    return {"architecture": "Darizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "layers": layers}
+
+
+def lfm3_like_config(z: dict) -> dict:
+    """The closest LFM3: every layer a sliding-window attention layer with the per-head gate."""
+    return {**CONFIG_1P2B, "hidden_size": z["width"], "num_hidden_layers": z["layers"],
+            "layer_types": ["sliding_attention"] * z["layers"], "num_attention_heads": z["heads"],
+            "num_key_value_heads": z["kv_heads"], "head_dim": z["dim"], "intermediate_size": z["ff"],
+            "vocab_size": z["vocab"], "sliding_window": z["window"],
+            "rope_parameters": {"sliding_attention": {"rope_type": "default", "rope_theta": 1000000.0}}}
+
+
+class _SizeOnly:
+    """What ``device_decode`` / ``device_prefill`` read of a configuration."""
+
+    def __init__(self, z: dict):
+        self.vocab_size, self.z = z["vocab"], z
+
+    def to_dict(self) -> dict:
+        return lfm3_like_config(self.z)
+
+
+def _timed_us(fn, flush, reps: int = 20) -> float:
+    import torch
+
+    times = []
+    for i in range(reps + 3):
+        flush.add_(1.0)                      # a pass over a buffer larger than L2
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        if i >= 3:
+            times.append(start.elapsed_time(end) * 1e3)
+    return statistics.median(times)
+
+
+def design_kernels(z: dict, pk: dict) -> list[dict]:
+    """Each kernel of the Darizen path beside the LFM3 kernel that does the like work, on the
+    same shapes (a 2,048-token prompt portion; 64 decoded tokens behind 2,048 positions), L2
+    flushed before every launch, CUDA events around one launch, median of 20. ``frac``: bytes
+    over time against the measured copy bandwidth (row-wise kernels, decode attention) or flops
+    over time against the measured bf16 rate (prompt attention)."""
+    import torch
+
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.rope import Rotary
+
+    bf, dev = torch.bfloat16, "cuda"
+    T, W, H, G, D, F, P, win = 2048, z["width"], z["heads"], z["kv_heads"], z["dim"], z["ff"], 16, z["window"]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    rows = []
+
+    def add(name, ours_us, theirs_us, ours_work, theirs_work, unit):
+        peak = pk["hbm_gbs"] * 1e3 if unit == "bytes" else pk["bf16_tflops"] * 1e6       # per microsecond
+        fo, ft = ours_work / ours_us / peak, theirs_work / theirs_us / peak
+        rows.append({"kernel": name, "darizen_us": round(ours_us, 1), "lfm3_us": round(theirs_us, 1),
+                     "darizen_frac": round(fo, 3), "lfm3_frac": round(ft, 3),
+                     "times_further_from_roofline": round(ft / fo, 2)})
+
+    x = torch.randn(T, W, device=dev).to(bf)
+    res16 = torch.randn(T, W, device=dev).to(bf)
+    res32 = torch.randn(T, W, device=dev)
+    w = torch.ones(W, device=dev)
+    add("residual add + norm",
+        _timed_us(lambda: ops.stream32_add_norm(res32, x, w, 1e-6), flush),
+        _timed_us(lambda: ops.add_rmsnorm(x, res16, w, 1e-6), flush),
+        T * W * (4 + 2 + 4 + 2), T * W * (2 + 2 + 2 + 2), "bytes")
+    gu = torch.randn(T, 2 * F, device=dev).to(bf)
+    add("gated activation",
+        _timed_us(lambda: ops.glu_clamped(gu, 7.0, 1.702, 1.0), flush),
+        _timed_us(lambda: ops.swiglu(gu, 0), flush), T * F * 6, T * F * 6, "bytes")
+    # rotation + cache write, then attention over the cache: one sequence of T positions
+    pages = T // P + 1
+    pool = torch.zeros(pages, 2, G, P, D, dtype=bf, device=dev)
+    table = torch.arange(1, pages, dtype=torch.int32, device=dev).view(1, -1)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    qkv = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+    rot = Rotary(D, D, 1e6, "half", {"kind": "linear", "factor": 8.0}, dev)
+    inv = (1.0 / (1e6 ** (torch.arange(0, D, 2, dtype=torch.float32) / D))).to(dev)
+    ones = torch.ones(D, device=dev)
+    add("rotation + cache write",
+        _timed_us(lambda: ops.rotary_write(qkv, pool, rot.freq, 1.0, pos, seq, table, H, G, D, D, P, False, False), flush),
+        _timed_us(lambda: ops.qk_norm_rope_write(qkv, pool, ones, ones, 1e-6, inv, pos, seq, table, H, G, D, P), flush),
+        T * (H + 2 * G) * D * 4, T * (H + 2 * G) * D * 4, "bytes")
+    q = ops.rotary_write(qkv, pool, rot.freq, 1.0, pos, seq, table, H, G, D, D, P, False, False)
+    out = torch.empty_like(q)
+    gate_e = torch.randn(T, H * D, device=dev).to(bf)
+    gate_h = torch.randn(T, H, device=dev).to(bf)
+    per = ops.attention_prefill_mma_tokens(H, G)
+    tok0 = torch.arange(0, T, per, dtype=torch.int32, device=dev)
+    ntok = torch.full_like(tok0, per)
+    visible = sum(min(i + 1, win) for i in range(T))
+    flops = 4.0 * visible * H * D
+    ours = _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, table, tok0, ntok, win, D ** -0.5,
+                                                       gate_e, 4, True, True), flush)
+    if ops.attention_prefill_tc_supported(H, G, D, bf):
+        per_tc = ops.attention_prefill_tc_tokens(H, G)
+        tok0_tc = torch.arange(0, T, per_tc, dtype=torch.int32, device=dev)
+        ntok_tc = torch.full_like(tok0_tc, per_tc)
+        theirs = _timed_us(lambda: ops.attention_prefill_tc(q, pool, out, pos, seq, table, tok0_tc, ntok_tc, win,
+                                                            D ** -0.5, gate_h, 1), flush)
+        like = "tcgen05"
+    else:
+        theirs = _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, table, tok0, ntok, win,
+                                                             D ** -0.5, gate_h), flush)
+        like = "mma.sync"
+    add(f"prompt attention (LFM3: {like})", ours, theirs, flops, flops, "flops")
+    plain = _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, table, tok0, ntok, win, D ** -0.5,
+                                                        gate_h), flush)
+    add("prompt attention (LFM3: mma.sync)", ours, plain, flops, flops, "flops")
+    # decode: B sequences of T cached positions each (they share the pages: the bytes are read per sequence)
+    B = 64
+    dpos = torch.full((B,), T - 1, dtype=torch.int32, device=dev)
+    dseq = torch.arange(B, dtype=torch.int32, device=dev)
+    dtable = table.expand(B, -1).contiguous()
+    dq, dout = q[:B].contiguous(), torch.empty_like(q[:B])
+    keys = min(T, win)
+    nsplit = 2
+    bytes_ = B * G * (keys + 4) * D * 2 * 2
+    add("decode attention, 64 tokens",
+        _timed_us(lambda: ops.attention_decode_mma(dq, pool, dout, dpos, dseq, dtable, None, win, D ** -0.5, nsplit,
+                                                   gate_e[:B], 4, True, True), flush),
+        _timed_us(lambda: ops.attention_decode_mma(dq, pool, dout, dpos, dseq, dtable, None, win, D ** -0.5, nsplit,
+                                                   gate_h[:B]), flush),
+        bytes_, B * G * keys * D * 2 * 2, "bytes")
+    return rows
+
+
+def run_design(name: str, args, warmup: int) -> int:
+    """``--design darizen``: decode (batch 8 and 64) and prefill (2,048 tokens) throughput of
+    Darizen stacks at a few real layer sizes, beside the LFM3 stack of sliding-window attention
+    layers at the same sizes, and a kernel-by-kernel table. One JSON line per size."""
+    import tempfile
+
+    import torch
+
+    from tokenomos_b200 import models
+    from tokenomos_b200.weights import write_model_folder
+
+    pk = peaks()
+    for size, z in DESIGN_SIZES.items():
+        line = {"design": name, "size": size, "sizes": z, "dtype": "bf16",
+                "data": "synthetic token ids, random-init weights N(0, 0.02)"}
+        for arm, config in (("darizen", darizen_config(z)), ("lfm3", lfm3_like_config(z))):
+            with tempfile.TemporaryDirectory(prefix="tokenomos_b200_design_") as tmp:
+                folder = Path(tmp) / arm
+                if arm == "darizen":
+                    write_model_folder(folder, config, 0, 0.02, 0.0, torch.bfloat16)
+                else:
+                    write_folder(folder, z["layers"], config)
+                model = models.load(str(folder), "cuda", models.configure(str(folder), work="bf16"))
+            cfg = _SizeOnly(z)
+            res = {}
+            for batch in (8, 64):
+                d = device_decode(model, cfg, batch, min(args.steps, 64), warmup, args.page)
+                res[f"decode_b{batch}"] = {"tok_s": round(d["tok_s"], 1), "ms_per_step": round(d["ms_per_step"], 4),
+                                           "launches": d["launches_per_step"]}
+            pf = device_prefill(model, cfg, args.page)
+            res["prefill_2048"] = {"tok_s": round(pf["tok_s"], 1), "ms": round(pf["ms"], 3),
+                                   "frac": round(pf["flops"] / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            line[arm] = res
+            del model
+            torch.cuda.empty_cache()
+        line["kernels"] = design_kernels(z, pk)
+        print(json.dumps(line), flush=True)
+    return 0
+
+
+
 METRIC = "decode tokens/s (1.2B-size LFM3, batch 8, context 2048+)"
 
 
@@ -904,6 +1104,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--trace", default=None,
                     help="--workload: write one JSON record per step of an extra pass to this file")
+    ap.add_argument("--design", default=None, choices=["darizen"],
+                    help="the named design beside the closest LFM3 configuration at equal sizes instead")
     ap.add_argument("--sweep", action="store_true",
                     help="decode and prefill at other batch sizes and context lengths instead")
     args = ap.parse_args()
@@ -931,6 +1133,8 @@ def main() -> int:
         return 0
     if args.workload:
         return run_workload(args.workload, args.page, args.trace)
+    if args.design:
+        return run_design(args.design, args, warmup)
     pk = peaks()
     import tempfile
 

@@ -82,15 +82,19 @@ CASES = {
 }
 # Bounds relative to the request's largest |logit|, about twice what a B200 measured. Against
 # the float64 plain implementation, 32-bit: A 2.2e-6, B 1.9e-6, C 1.7e-6, D 1.4e-5 (D runs its
-# loud layers three times); bfloat16: A 2.2 %, B 2.3 %, C 3.4 %, D 10 %. Between two ways of
-# cutting the same run, 32-bit: at most 6.7e-6; bfloat16: A 0.18 %, B 0.3 %, C 1e-7
-# where the general attention kernel runs (a decoded token and a prompt portion round alike but
-# for the order of its sums); D takes the tensor-core kernels, whose prompt and decode forms round
-# the softmax's weights to 16 bits against different running maxima: 4.2 %.
+# loud layers three times); bfloat16: A 2.2 %, B 2.6 %, C 3.4 %, D 10 %. Between two ways of
+# cutting the same run, 32-bit: at most 6.7e-6. Two bfloat16 runs that differ only in cutting do
+# not round alike: a step of a few decoded tokens computes the feed-forward's activation in the
+# epilogue of the gate/up product, from 32-bit sums, where a prompt portion rounds gate and up to
+# 16 bits first, and the tensor-core attention (D) rounds the softmax's weights against other
+# running maxima in its prompt and decode forms. Their difference is that of two roundings of the
+# same values and is held to about the bound each has against the plain implementation
+# (measured: A 1.2 %, B 1.1 %, C 0.54 %, D 4.2 %); the 32-bit path, where the cut changes no
+# rounding, is what holds the cache and the batch to 2e-5.
 TOL_F32 = {"A": 1e-5, "B": 1e-5, "C": 1e-5, "D": 4e-5}
 TOL_F32_SAME = {"A": 5e-6, "B": 5e-6, "C": 2e-6, "D": 2e-5}
 TOL_BF16 = {"A": 4.5e-2, "B": 4.5e-2, "C": 6e-2, "D": 0.2}
-TOL_BF16_SAME = {"A": 4e-3, "B": 6e-3, "C": 1e-3, "D": 8e-2}
+TOL_BF16_SAME = {"A": 2.5e-2, "B": 2.5e-2, "C": 1.2e-2, "D": 8e-2}
 
 
 def make_tensors(config: dict, seed: int) -> dict[str, torch.Tensor]:
@@ -313,6 +317,24 @@ def test_clamped_glu_and_sigmoid_gate(dtype):
         tol = 1e-6 if dtype == torch.float32 else 2 ** -8
         assert (got - want).abs().max() <= tol * want.abs().max()
     assert (gu.double().abs() > 1.5).any()           # the clamp was at work
+    # gate and up in runs of 8 channels, and the same activation in a small product's epilogue
+    inter = 48
+    gu = (torch.randn(rows, 2 * inter) * 3).to(dtype)
+    runs = torch.stack((gu[:, :inter].view(rows, -1, 8), gu[:, inter:].view(rows, -1, 8)), dim=2).reshape(rows, -1)
+    assert torch.equal(ops.glu_clamped(dev(runs, dtype), 1.5, 1.702, 1.0, 8), ops.glu_clamped(dev(gu, dtype), 1.5, 1.702, 1.0))
+    if dtype == torch.bfloat16:
+        from tokenomos_b200.parts.ffn import interleave_rows
+        k = 64
+        x = torch.randn(rows, k).to(dtype)
+        wg, wu = (torch.randn(inter, k) * 0.3).to(dtype), (torch.randn(inter, k) * 0.3).to(dtype)
+        bg, bu = torch.randn(inter).to(dtype).float(), torch.randn(inter).to(dtype).float()
+        w = interleave_rows(wg, wu, 8)
+        bias = interleave_rows(bg.view(-1, 1), bu.view(-1, 1), 8).view(-1)
+        got = ops.gemm_skinny_glu(dev(x, dtype), dev(w, dtype), dev(bias), 1.5, 1.702, 1.0).cpu().double()
+        g = torch.clamp(x.double() @ wg.double().T + bg.double(), max=1.5)
+        u = torch.clamp(x.double() @ wu.double().T + bu.double(), -1.5, 1.5)
+        want = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+        assert (got - want).abs().max() <= 2 ** -8 * want.abs().max()
     x = torch.randn(rows, 3, 10).to(dtype)
     wide = torch.randn(rows, 50).to(dtype)
     got = ops.sigmoid_gate(dev(x, dtype), dev(wide, dtype)[:, 11:41]).cpu().double()

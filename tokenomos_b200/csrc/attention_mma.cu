@@ -74,7 +74,12 @@ struct AttnOptions {
 
 __device__ __forceinline__ float elem_gate_of(const __nv_bfloat16* gate, int64_t ldg, int tok, int col) {
     const float g = __bfloat162float(gate[(size_t)tok * ldg + col]);
-    return 1.0f / (1.0f + expf(-g));
+    return 1.0f / (1.0f + __expf(-g));
+}
+// two neighbouring elements' gates with one load (col even, rows an even number of elements apart)
+__device__ __forceinline__ float2 elem_gate_pair(const __nv_bfloat16* gate, int64_t ldg, int tok, int col) {
+    const float2 g = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gate + (size_t)tok * ldg + col));
+    return make_float2(1.0f / (1.0f + __expf(-g.x)), 1.0f / (1.0f + __expf(-g.y)));
 }
 
 // One 16-row x NK-key block of the online softmax for a warp: S = Q K^T from `ktile`, mask,
@@ -343,9 +348,9 @@ attn_prefill_mma_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool,
         for (int n = 0; n < D / 8; ++n) {
             if (by_element) {
                 const int col = (kvh * G + r % G) * D + n * 8 + 2 * t;
+                const float2 gp = elem_gate_pair(gate, ldg, tok0 + r / G, col);
                 *reinterpret_cast<uint32_t*>(dst + n * 8 + 2 * t) =
-                    pack_bf16(o[n][half * 2] * inv * elem_gate_of(gate, ldg, tok0 + r / G, col),
-                              o[n][half * 2 + 1] * inv * elem_gate_of(gate, ldg, tok0 + r / G, col + 1));
+                    pack_bf16(o[n][half * 2] * inv * gp.x, o[n][half * 2 + 1] * inv * gp.y);
                 continue;
             }
             uint32_t v = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
@@ -941,6 +946,8 @@ TK_API int tk_attn_prefill_mma_opt(const void* q, const void* kv_pool, void* out
     TK_CHECK_ARG(keep_first >= 0 && (keep_first == 0 || window > 0), "attn_prefill_mma: kept first positions need a window");
     TK_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0) == (gate == nullptr),
                  "attn_prefill_mma: gate mode %d and the gate do not go together", gate_mode);
+    TK_CHECK_ARG(gate_mode != 2 || (ldg % 2 == 0 && (uintptr_t)gate % 4 == 0),
+                 "attn_prefill_mma: a gate per element is read two at a time: even row distance, 4-byte aligned");
     const AttnOptions opt{keep_first, sink ? 1 : 0, gate_mode};
     TK_CHECK_ARG(mma_shape_ok(H, Hkv, D), "attn_prefill_mma: shape H=%d Hkv=%d D=%d is not taken "
                  "(head size 64 or 128, group a power of two up to 16)", H, Hkv, D);

@@ -73,6 +73,11 @@ struct Fuse {
     float eps;                          // NORM
     const __nv_bfloat16* residual;      // ADD: [M, N], rows `ldr` apart
     int64_t ldr;
+    // EPI_SWIGLU with another activation (glu != 0): g = min(gate, limit), u = clamp(up, -limit,
+    // limit) (limit <= 0: no clamp), out = g * sigmoid(alpha g) * (u + shift), from the 32-bit
+    // sums, rounded once
+    int glu;
+    float glu_limit, glu_alpha, glu_shift;
 };
 
 __device__ __forceinline__ float sum_squares(const uint4& v) {
@@ -322,6 +327,15 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
                 gate += bias[n0 + j];
                 up += bias[n0 + 8 + j];
             }
+            if (fuse.glu) {
+                if (fuse.glu_limit > 0.f) {
+                    gate = fminf(gate, fuse.glu_limit);
+                    up = fminf(fmaxf(up, -fuse.glu_limit), fuse.glu_limit);
+                }
+                out[(size_t)tok * ldo + n0 / 2 + j] =
+                    from_f<TO>(gate / (1.0f + __expf(-fuse.glu_alpha * gate)) * (up + fuse.glu_shift));
+                continue;
+            }
             // the unfused path stores gate and up in the output type, then rounds silu(gate)
             gate = round_as<TO>(gate);
             up = round_as<TO>(up);
@@ -362,9 +376,10 @@ gemm_skinny_kernel(const __nv_bfloat16* x, int64_t ldx,
 // by each row's 1 / sqrt(mean(x^2) + norm_eps) (see Fuse; the norm's weight is in w's columns).
 // residual != null (at most 8 rows, bfloat16 out, no swiglu): out = residual + product, the
 // product rounded first, the sum rounded once; residual: [M, N] bfloat16, rows `ldr` apart.
-TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
-                          void* out, int64_t ldo, int M, int N, int K, int out_dtype, int swiglu,
-                          float norm_eps, const void* residual, int64_t ldr, cudaStream_t stream) {
+static int skinny_launch(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+                         void* out, int64_t ldo, int M, int N, int K, int out_dtype, int swiglu,
+                         float norm_eps, const void* residual, int64_t ldr, int glu, float glu_limit,
+                         float glu_alpha, float glu_shift, cudaStream_t stream) {
     TK_CHECK_ARG(M >= 0 && M <= 16 && N > 0 && K > 0, "gemm_skinny: M=%d (at most 16) N=%d K=%d", M, N, K);
     TK_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "gemm_skinny: K and the leading dimensions "
                  "must be multiples of 8 (K=%d)", K);
@@ -393,7 +408,7 @@ TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw
     const size_t smem = ((size_t)warps * ROWS * MT + (norm ? (size_t)warps * MT + MT : 0)) * sizeof(float);
     auto x_ = (const __nv_bfloat16*)x;
     auto w_ = (const __nv_bfloat16*)w;
-    const Fuse fuse{norm_eps, (const __nv_bfloat16*)residual, ldr};
+    const Fuse fuse{norm_eps, (const __nv_bfloat16*)residual, ldr, glu, glu_limit, glu_alpha, glu_shift};
 #define TK_SKINNY_F(MT_, TO_, R8_, SW_, NORM_, ADD_)                                               \
     do {                                                                                           \
         if (unroll == 2)                                                                           \
@@ -425,6 +440,24 @@ TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw
 #undef TK_SKINNY_F
     TK_CHECK_LAUNCH("gemm_skinny");
     return 0;
+}
+
+TK_API int tk_gemm_skinny(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+                          void* out, int64_t ldo, int M, int N, int K, int out_dtype, int swiglu,
+                          float norm_eps, const void* residual, int64_t ldr, cudaStream_t stream) {
+    return skinny_launch(x, ldx, w, ldw, bias, out, ldo, M, N, K, out_dtype, swiglu, norm_eps, residual, ldr, 0, 0.f,
+                         0.f, 0.f, stream);
+}
+
+// The gate/up product with a clamped gated activation in its epilogue: w's rows alternate in runs
+// of 8 (8 gate rows, the 8 up rows of the same channels; N a multiple of 16), bias likewise;
+// out [M, N / 2] = g * sigmoid(alpha g) * (u + shift) with g = min(gate, limit), u = clamp(up,
+// -limit, limit) (limit <= 0: no clamp), computed from the 32-bit sums and rounded once.
+TK_API int tk_gemm_skinny_glu(const void* x, int64_t ldx, const void* w, int64_t ldw, const float* bias,
+                              void* out, int64_t ldo, int M, int N, int K, int out_dtype, float limit,
+                              float alpha, float shift, cudaStream_t stream) {
+    return skinny_launch(x, ldx, w, ldw, bias, out, ldo, M, N, K, out_dtype, 1, 0.f, nullptr, 0, 1, limit, alpha, shift,
+                         stream);
 }
 
 // The in-projection of a gated short conv with the conv in its epilogue, for a step in which every

@@ -58,12 +58,110 @@ stream32_add_norm_kernel(const float* stream_in, const T* x, int64_t x_stride, c
     }
 }
 
+// The same with 16 bytes of the stream (four elements) per thread and step, the row in registers:
+// one trip to memory. Needs width % 4 == 0, rows of x a multiple of four elements apart, every
+// base 16-byte aligned (8-byte for 16-bit inputs), and width <= 4 * ITEMS * blockDim.
+template <typename T>
+struct Quad {
+    static __device__ __forceinline__ float4 load(const T* p);
+    static __device__ __forceinline__ void store(T* p, float4 v);
+};
+template <>
+struct Quad<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <>
+struct Quad<__nv_bfloat16> {
+    static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<const uint32_t*>(&a);
+        raw.y = *reinterpret_cast<const uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T, int ITEMS>
+__global__ void __launch_bounds__(256)
+stream32_add_norm_vec_kernel(const float* stream_in, const T* x, int64_t x_stride, const T* rows_add,
+                             const float* __restrict__ vec_add, const float* __restrict__ w, float eps,
+                             float* stream_out, T* y, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    float4 keep[ITEMS];
+    float ss = 0.f;
+    // every load of the row is asked for before the first sum
+    float4 a[ITEMS], b[ITEMS], c[ITEMS];
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        a[k] = b[k] = c[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < width) {
+            if (stream_in != nullptr) a[k] = *reinterpret_cast<const float4*>(stream_in + r * width + i);
+            if (x != nullptr) b[k] = Quad<T>::load(x + r * x_stride + i);
+            if (rows_add != nullptr) c[k] = Quad<T>::load(rows_add + r * width + i);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < width) {
+            // (the same order of sums as the scalar kernel: stream, x, rows, vector)
+            v = a[k];
+            if (x != nullptr) v = make_float4(v.x + b[k].x, v.y + b[k].y, v.z + b[k].z, v.w + b[k].w);
+            if (rows_add != nullptr) v = make_float4(v.x + c[k].x, v.y + c[k].y, v.z + c[k].z, v.w + c[k].w);
+            if (vec_add != nullptr) {
+                const float4 d = *reinterpret_cast<const float4*>(vec_add + i);
+                v = make_float4(v.x + d.x, v.y + d.y, v.z + d.z, v.w + d.w);
+            }
+            if (stream_out != nullptr) *reinterpret_cast<float4*>(stream_out + r * width + i) = v;
+        }
+        keep[k] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    if (w == nullptr) return;
+    const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+#pragma unroll
+    for (int k = 0; k < ITEMS; ++k) {
+        const int i = (threadIdx.x + k * blockDim.x) * 4;
+        if (i < width) {
+            const float4 g = *reinterpret_cast<const float4*>(w + i);
+            Quad<T>::store(y + r * width + i, make_float4(keep[k].x * rstd * g.x, keep[k].y * rstd * g.y,
+                                                           keep[k].z * rstd * g.z, keep[k].w * rstd * g.w));
+        }
+    }
+}
+
 template <typename T>
 static int launch_stream32(const float* stream_in, const void* x, int64_t x_stride, const void* rows_add,
                            const float* vec_add, const float* w, float eps, float* stream_out, void* y,
                            int rows, int width, cudaStream_t stream) {
     const int threads = width >= 1024 ? 256 : 128;
     const int per_thread = (width + threads - 1) / threads;
+    auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    const bool vec = width % 4 == 0 && x_stride % 4 == 0 && aligned(stream_in) && aligned(stream_out) &&
+                     aligned(vec_add) && aligned(w) && ((uintptr_t)x & 7) == 0 && ((uintptr_t)rows_add & 7) == 0 &&
+                     ((uintptr_t)y & 7) == 0 && (sizeof(T) == 2 || (aligned(x) && aligned(rows_add) && aligned(y)));
+    if (vec && width <= 4 * 2 * threads) {
+        tk_launch(stream32_add_norm_vec_kernel<T, 2>, dim3(rows), dim3(threads), 0, stream, stream_in, (const T*)x,
+                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, width);
+        return 0;
+    }
+    if (vec && width <= 4 * 6 * threads) {
+        tk_launch(stream32_add_norm_vec_kernel<T, 6>, dim3(rows), dim3(threads), 0, stream, stream_in, (const T*)x,
+                  x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, width);
+        return 0;
+    }
     if (per_thread <= 8)
         tk_launch(stream32_add_norm_kernel<T, 8>, dim3(rows), dim3(threads), 0, stream, stream_in, (const T*)x,
                   x_stride, (const T*)rows_add, vec_add, w, eps, stream_out, (T*)y, width);
@@ -98,18 +196,20 @@ TK_API int tk_stream32_add_norm(const float* stream_in, const void* x, int64_t x
 
 // ---------------------------------------------------------------------------------------------
 // clamped gated activation: g = min(gate, limit), u = clamp(up, -limit, limit),
-// out = g * sigmoid(alpha * g) * (u + shift); gu = [gate (inter) | up (inter)] per row.
-// limit <= 0: no clamp.
+// out = g * sigmoid(alpha * g) * (u + shift); gu = [gate (inter) | up (inter)] per row, or
+// (block > 0) gate and up alternating in runs of `block` channels, the layout a decode product
+// with the activation in its epilogue wants of the weight rows. limit <= 0: no clamp.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void glu_clamped_kernel(const T* gu, T* out, int inter, float limit, float alpha, float shift) {
+__global__ void glu_clamped_kernel(const T* gu, T* out, int inter, int block, float limit, float alpha, float shift) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t t = blockIdx.x;
     const T* row = gu + t * 2 * inter;
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < inter; c += gridDim.y * blockDim.x) {
-        float g = to_f<T>(row[c]);
-        float u = to_f<T>(row[inter + c]);
+        const int gi = block > 0 ? (c / block) * 2 * block + c % block : c;
+        float g = to_f<T>(row[gi]);
+        float u = to_f<T>(row[block > 0 ? gi + block : inter + c]);
         if (limit > 0.f) {
             g = fminf(g, limit);
             u = fminf(fmaxf(u, -limit), limit);
@@ -118,18 +218,63 @@ __global__ void glu_clamped_kernel(const T* gu, T* out, int inter, float limit, 
     }
 }
 
-TK_API int tk_glu_clamped(const void* gu, void* out, int rows, int inter, float limit, float alpha, float shift,
-                          int dtype, cudaStream_t stream) {
+// 16 bytes of gate and of up per thread (bfloat16, inter % 8 == 0): the sigmoid through the
+// special-function unit's exponential and reciprocal, whose error (a few ulp of a float) is far
+// below the one 16-bit rounding that follows.
+__global__ void __launch_bounds__(256)
+glu_clamped_vec_kernel(const __nv_bfloat16* gu, __nv_bfloat16* out, int inter, int block, float limit, float alpha,
+                       float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t t = blockIdx.x;
+    const __nv_bfloat16* row = gu + t * 2 * inter;
+    const float k = -alpha * 1.4426950408889634f;
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < inter; c += gridDim.y * blockDim.x * 8) {
+        const int gi = block > 0 ? (c / block) * 2 * block + c % block : c;
+        const uint4 graw = *reinterpret_cast<const uint4*>(row + gi);
+        const uint4 uraw = *reinterpret_cast<const uint4*>(row + (block > 0 ? gi + block : inter + c));
+        const uint32_t* g2 = reinterpret_cast<const uint32_t*>(&graw);
+        const uint32_t* u2 = reinterpret_cast<const uint32_t*>(&uraw);
+        uint4 packed;
+        uint32_t* o2 = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float2 g = make_float2(__uint_as_float(g2[e] << 16), __uint_as_float(g2[e] & 0xffff0000u));
+            float2 u = make_float2(__uint_as_float(u2[e] << 16), __uint_as_float(u2[e] & 0xffff0000u));
+            if (limit > 0.f) {
+                g.x = fminf(g.x, limit), g.y = fminf(g.y, limit);
+                u.x = fminf(fmaxf(u.x, -limit), limit), u.y = fminf(fmaxf(u.y, -limit), limit);
+            }
+            const float a = g.x * rcp_approx(1.0f + ex2_approx(g.x * k)) * (u.x + shift);
+            const float b = g.y * rcp_approx(1.0f + ex2_approx(g.y * k)) * (u.y + shift);
+            const __nv_bfloat162 r = __floats2bfloat162_rn(a, b);
+            o2[e] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        *reinterpret_cast<uint4*>(out + t * inter + c) = packed;
+    }
+}
+
+TK_API int tk_glu_clamped(const void* gu, void* out, int rows, int inter, int block, float limit, float alpha,
+                          float shift, int dtype, cudaStream_t stream) {
     TK_CHECK_ARG(rows >= 0 && inter > 0, "glu_clamped: bad sizes rows=%d inter=%d", rows, inter);
+    TK_CHECK_ARG(block >= 0 && (block == 0 || inter % block == 0), "glu_clamped: runs of %d channels do not divide %d",
+                 block, inter);
     if (rows == 0) return 0;
     const int threads = 256;
     const dim3 grid(rows, min(ceil_div(inter, threads), 64));
+    if (dtype == TK_BF16 && inter % 8 == 0 && (block == 0 || block % 8 == 0) && (uintptr_t)gu % 16 == 0 &&
+        (uintptr_t)out % 16 == 0) {
+        tk_launch(glu_clamped_vec_kernel, dim3(rows, min(ceil_div(inter, threads * 8), 64)), dim3(threads), 0, stream,
+                  (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, block, limit, alpha, shift);
+        TK_CHECK_LAUNCH("glu_clamped_vec");
+        return 0;
+    }
     if (dtype == TK_F32)
-        tk_launch(glu_clamped_kernel<float>, grid, dim3(threads), 0, stream, (const float*)gu, (float*)out, inter, limit,
-                  alpha, shift);
+        tk_launch(glu_clamped_kernel<float>, grid, dim3(threads), 0, stream, (const float*)gu, (float*)out, inter, block,
+                  limit, alpha, shift);
     else if (dtype == TK_BF16)
         tk_launch(glu_clamped_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)gu,
-                  (__nv_bfloat16*)out, inter, limit, alpha, shift);
+                  (__nv_bfloat16*)out, inter, block, limit, alpha, shift);
     else
         TK_CHECK_ARG(false, "glu_clamped: unknown dtype %d", dtype);
     TK_CHECK_LAUNCH("glu_clamped");

@@ -15,7 +15,7 @@ from tokenomos_b200.ops._lib import BF16, F32, KernelError
 
 __all__ = [
     "KernelError", "available", "checks_enabled", "set_check_bounds", "checks_status", "gather_rows", "add_rmsnorm", "swiglu", "head_gate",
-    "qk_norm_rope_write", "rotary_write", "stream32_add_norm", "glu_clamped", "sigmoid_gate", "attention", "attention_rows", "attention_mma_supported",
+    "qk_norm_rope_write", "rotary_write", "stream32_add_norm", "glu_clamped", "gemm_skinny_glu", "sigmoid_gate", "attention", "attention_rows", "attention_mma_supported",
     "attention_prefill_mma", "attention_prefill_mma_tokens", "attention_decode_mma",
     "attention_prefill_tc", "attention_prefill_tc_supported", "attention_prefill_tc_tokens",
     "attention_prefill_tc_status",
@@ -348,16 +348,35 @@ def stream32_add_norm(stream: torch.Tensor | None, x: torch.Tensor | None, weigh
     return y, out
 
 
-def glu_clamped(gu: torch.Tensor, limit: float | None, alpha: float, shift: float) -> torch.Tensor:
+def glu_clamped(gu: torch.Tensor, limit: float | None, alpha: float, shift: float, block: int = 0) -> torch.Tensor:
     """``g * sigmoid(alpha g) * (u + shift)`` with ``g = min(gate, limit)``, ``u = clamp(up,
-    -limit, limit)`` for ``gu = [gate | up]`` of width ``2 I`` (``limit`` None: no clamp)."""
+    -limit, limit)`` for ``gu = [gate | up]`` of width ``2 I`` (``limit`` None: no clamp);
+    ``block`` > 0: gate and up alternate in runs of ``block`` channels instead."""
     _cuda(gu)
     if not gu.is_contiguous() or gu.shape[1] % 2:
         raise KernelError("glu_clamped: input must be contiguous with an even width")
     rows, inter = gu.shape[0], gu.shape[1] // 2
     out = torch.empty(rows, inter, dtype=gu.dtype, device=gu.device)
-    _lib.call("tk_glu_clamped", _ptr(gu), _ptr(out), rows, inter, float(limit or 0.0), float(alpha), float(shift),
-              _dtype_code(gu), _stream())
+    _lib.call("tk_glu_clamped", _ptr(gu), _ptr(out), rows, inter, int(block), float(limit or 0.0), float(alpha),
+              float(shift), _dtype_code(gu), _stream())
+    return out
+
+
+def gemm_skinny_glu(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, limit: float | None,
+                    alpha: float, shift: float) -> torch.Tensor:
+    """The gate/up product of at most 16 rows with the clamped gated activation (``glu_clamped``)
+    in its epilogue: ``w``'s rows (and ``bias``) alternate in runs of 8 (8 gate rows, the 8 up rows
+    of the same channels); the activation is computed from the 32-bit sums and rounded once.
+    Returns [M, N / 2]."""
+    _cuda(x, w, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or N % 16 or not gemm_skinny_ok(x, w):
+        raise KernelError(f"gemm_skinny_glu: x {tuple(x.shape)} against w {tuple(w.shape)}")
+    out = torch.empty(M, N // 2, dtype=x.dtype, device=x.device)
+    _lib.call("tk_gemm_skinny_glu", _ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(_f32vec(bias, "bias", N)),
+              _ptr(out), out.stride(0), M, N, K, _dtype_code(out), float(limit or 0.0), float(alpha), float(shift),
+              _stream())
     return out
 
 

@@ -38,7 +38,8 @@ _SIGNATURES = {
     "tk_attn_generic": [P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, I, I, I, F, I, P],
     "tk_rotary_write": [P, L, P, P, P, F, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P],
     "tk_stream32_add_norm": [P, P, L, P, P, P, F, P, P, I, I, I, P],
-    "tk_glu_clamped": [P, P, I, I, F, F, F, I, P],
+    "tk_glu_clamped": [P, P, I, I, I, F, F, F, I, P],
+    "tk_gemm_skinny_glu": [P, L, P, L, P, P, L, I, I, I, I, F, F, F, P],
     "tk_sigmoid_gate": [P, P, L, I, I, I, P],
     "tk_attn_mma_supported": [I, I, I],
     "tk_attn_prefill_mma_tokens": [I, I],

@@ -84,22 +84,37 @@ class ClampedGLU:
     capture_safe = True
 
     def __init__(self, gate_up: Linear, down: Linear, limit: float | None, alpha: float = 1.0,
-                 shift: float = 0.0):
+                 shift: float = 0.0, run: int = 0):
+        """``run`` 0: ``gate_up``'s rows are all gate rows, then all up rows; ``run`` 8: they
+        alternate in runs of 8 channels (as ``SwiGLU``'s), and a step of a few tokens computes
+        the activation in the product's epilogue."""
         if gate_up.out_features != 2 * down.in_features:
             raise ValueError("ClampedGLU: gate_up must be twice as wide as down's input")
         if limit is not None and limit <= 0:
             raise ValueError(f"ClampedGLU: a limit of {limit}: it must be positive")
-        self.gate_up, self.down = gate_up, down
+        self.gate_up, self.down, self.run = gate_up, down, run
         self.limit, self.alpha, self.shift = limit, float(alpha), float(shift)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down(ops.glu_clamped(self.gate_up(x), self.limit, self.alpha, self.shift))
+        w = self.gate_up.weight
+        if (self.run == RUN and x.shape[0] <= self.gate_up.tuning.swiglu_fused_rows and ops.gemm_skinny_ok(x, w)):
+            self.gate_up.note("skinny+glu")
+            act = ops.gemm_skinny_glu(x, w, self.gate_up.bias, self.limit, self.alpha, self.shift)
+        else:
+            act = ops.glu_clamped(self.gate_up(x), self.limit, self.alpha, self.shift, self.run)
+        return self.down(act)
 
 
 @register("feed_forward", "glu_clamped")
 def build_clamped_glu(params: dict, tensors: dict, rt: Runtime) -> ClampedGLU:
+    gate, up = tensors["gate"], tensors["up"]
     biases = [tensors.get("gate_bias"), tensors.get("up_bias")]
-    gate_up = Linear.fused([tensors["gate"], tensors["up"]], biases if biases[0] is not None else None,
-                           tuning=rt.tuning)
-    return ClampedGLU(gate_up, Linear(tensors["down"], tensors.get("down_bias"), tuning=rt.tuning),
-                      params.get("limit"), params.get("alpha", 1.0), params.get("shift", 0.0))
+    down = Linear(tensors["down"], tensors.get("down_bias"), tuning=rt.tuning)
+    args = (params.get("limit"), params.get("alpha", 1.0), params.get("shift", 0.0))
+    if gate.dtype == torch.bfloat16 and gate.shape[0] % RUN == 0:
+        bias = None
+        if biases[0] is not None:
+            bias = interleave_rows(biases[0].float().view(-1, 1), biases[1].float().view(-1, 1), RUN).view(-1)
+        return ClampedGLU(Linear(interleave_rows(gate, up, RUN), bias, tuning=rt.tuning), down, *args, run=RUN)
+    gate_up = Linear.fused([gate, up], biases if biases[0] is not None else None, tuning=rt.tuning)
+    return ClampedGLU(gate_up, down, *args)

@@ -30,6 +30,13 @@ class Linear:
         ``tuning``: the thresholds ``route`` picks kernels by."""
         self.weight = weight.contiguous()
         self.bias = bias.float().contiguous() if bias is not None else None
+        # the bias in the matrix's 16-bit type, when that loses nothing (a bias stored in 16 bits
+        # widens and narrows exactly): the library's product then adds it to its 32-bit sum itself
+        self.bias16 = None
+        if self.bias is not None and weight.dtype == torch.bfloat16:
+            narrow = self.bias.to(weight.dtype)
+            if torch.equal(narrow.float(), self.bias):
+                self.bias16 = narrow.contiguous()
         self.out_features, self.in_features = weight.shape
         self.tuning = tuning
         # which route took how many products (tests read it to see that every branch ran)
@@ -73,8 +80,11 @@ class Linear:
             return ops.gemm_skinny(x, w, self.bias, out_dtype)
         if route == "simt":
             return ops.gemm(x, w, self.bias, out_dtype or x.dtype)
-        # the library's product has no 32-bit bias: the bias is added to the 32-bit result and
-        # the sum rounded once, as every other route does
+        # a bias that is exact in 16 bits rides in the library's epilogue (added to the 32-bit sum,
+        # one rounding); any other is added to the 32-bit result and the sum rounded once, as
+        # every other route does
+        if out_dtype != torch.float32 and self.bias16 is not None:
+            return F.linear(x, w, self.bias16)
         if out_dtype == torch.float32 or self.bias is not None:
             y = torch.mm(x, w.t(), out_dtype=torch.float32)
             if self.bias is not None:
