@@ -46,9 +46,6 @@ class Attention:
             raise ValueError(f"attention: gate kind {gate_kind!r}: 'head' or 'element'")
         if keep_first and window is None:
             raise ValueError("attention: kept first positions need a window")
-        if v_dim > ops.ATTENTION_MAX_HEAD_DIM:
-            raise ValueError(f"attention: a value size of {v_dim} is above the "
-                             f"{ops.ATTENTION_MAX_HEAD_DIM} the attention kernels take")
         self.sink, self.keep_first, self.v_dim, self.v_is_k = bool(sink), int(keep_first), v_dim, bool(v_is_k)
         self.gate_kind, self.exact = gate_kind, bool(exact)
         # what the one-kernel decode form, the tcgen05 prefill kernel and the norms folded into
@@ -60,6 +57,9 @@ class Attention:
             raise ValueError(f"{heads} query heads over {kv_heads} KV heads")
         if head_dim > ops.ATTENTION_MAX_HEAD_DIM:
             raise ValueError(f"attention: a head size of {head_dim} is above the "
+                             f"{ops.ATTENTION_MAX_HEAD_DIM} the attention kernels take")
+        if v_dim > ops.ATTENTION_MAX_HEAD_DIM:
+            raise ValueError(f"attention: a value size of {v_dim} is above the "
                              f"{ops.ATTENTION_MAX_HEAD_DIM} the attention kernels take")
         self.qkv, self.o, self.gate = qkv, o, gate
         self.heads, self.kv_heads, self.head_dim = heads, kv_heads, head_dim
