@@ -195,11 +195,14 @@ def test_declaration_lists_the_layer_runs_and_the_tensors():
                                                            (1, 2), (2, None)]
     names = {d.name: d.shape for d in spec.tensor_decls()}
     assert names["loop.step"] == (3, 128) and names["l0.mix.v"] == (128, 128) and names["l0.mix.q.b"] == (512,)
-    assert "l1.mix.v" not in names and "l1.mix.q.b" not in names and "l2.norm2" not in names
+    assert "l1.mix.v" not in names and "l1.mix.q.b" not in names
     assert names["l1.mix.g"] == (512, 128) and names["l1.mlp.down.b"] == (128,) and names["head"] == (400, 128)
     # no loop: no stack tensor, the layers once
     spec = arch.declare(arch.config_class.from_dict(DZ_C))
     assert [c.block for c in spec.order] == [0] and not spec.extras
+    # a layer without a feed-forward may still store a second norm: optional, read by nothing
+    spec_d = arch.declare(arch.config_class.from_dict(DZ_D))
+    assert [d.name for d in spec_d.tensor_decls() if d.optional] == ["l2.norm2"]
     # a loop from the first layer: the first pass adds its row, not the embedding
     spec = arch.declare(arch.config_class.from_dict(DZ_A))
     assert [(c.block, bool(c.add)) for c in spec.order] == [(0, True), (1, False), (0, True), (1, False), (2, False)]

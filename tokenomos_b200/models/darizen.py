@@ -87,6 +87,9 @@ class Darizen:
             }))
 
         n = len(blocks)
+        # a folder may store the second norm of a layer that has no feed-forward: nothing reads it
+        unused = tuple((f"unused.l{i}.norm2", TensorDecl(f"l{i}.norm2", (d,), ROLE_VECTOR, optional=True))
+                       for i, layer in enumerate(cfg.layers) if layer.mlp is None)
         order, extras = [], ()
         if cfg.loop is None:
             order = [LayerCall(i) for i in range(n)]
@@ -107,5 +110,5 @@ class Darizen:
             order=tuple(order),
             final_norm=norm("final.norm"),
             head=TensorDecl("head", (cfg.vocab, d), ROLE_MATRIX),
-            extras=extras,
+            extras=extras + unused,
         )
