@@ -379,11 +379,18 @@ class PagedSequence:
                 ops.attention_decode_mma(qr, self.pool, out, positions, seq, self.table, None, window, scale, nsplit,
                                          None, keep_first, sink)
             else:
-                per_tile = ops.attention_prefill_mma_tokens(self.H, self.G)
+                tcgen05 = tensor_cores == "tcgen05"
+                per_tile = (ops.attention_prefill_tc_tokens if tcgen05 else ops.attention_prefill_mma_tokens)(
+                    self.H, self.G)
                 tok0 = torch.arange(0, n, per_tile, dtype=torch.int32, device="cuda")
                 ntok = torch.clamp(n - tok0, max=per_tile).to(torch.int32)
-                ops.attention_prefill_mma(qr, self.pool, out, positions, seq, self.table, tok0, ntok, window, scale,
-                                          None, keep_first, sink)
+                if tcgen05:
+                    ops.attention_prefill_tc(qr, self.pool, out, positions, seq, self.table, tok0, ntok, window, scale,
+                                             None, nsplit, keep_first, sink)
+                    assert ops.attention_prefill_tc_status() == 0
+                else:
+                    ops.attention_prefill_mma(qr, self.pool, out, positions, seq, self.table, tok0, ntok, window,
+                                              scale, None, keep_first, sink)
             return out.cpu().double()
         per_tile = max(1, ops.attention_rows() // (self.H // self.G))
         tok0 = torch.arange(0, n, per_tile, dtype=torch.int32, device="cuda")
@@ -416,6 +423,9 @@ def cuts_of(T: int, how: str) -> list[int]:
     dict(H=8, G=2, Dk=64, Dv=64, page=16, window=40, keep=5, interleaved=False, v_is_k=False, dims=32, tc=True),
     dict(H=4, G=2, Dk=128, Dv=128, page=16, window=24, keep=0, interleaved=True, v_is_k=True, dims=64, tc=True),
     dict(H=4, G=1, Dk=64, Dv=64, page=8, window=70, keep=66, interleaved=False, v_is_k=False, dims=16, tc=True),
+    # the tcgen05 prompt kernel (head size 64), whole tiles of 128 rows and ragged ones, keys shared by several CTAs
+    dict(H=8, G=2, Dk=64, Dv=64, page=16, window=40, keep=5, interleaved=False, v_is_k=False, dims=32, tc="tcgen05"),
+    dict(H=4, G=4, Dk=64, Dv=64, page=16, window=150, keep=70, interleaved=True, v_is_k=True, dims=32, tc="tcgen05"),
 ])
 def test_rotation_cache_and_attention_with_one_loud_key(case, dtype, how):
     """One key is made loud for every query (a score of about 12 against a spread of 1), so a row
@@ -458,7 +468,7 @@ def test_rotation_cache_and_attention_with_one_loud_key(case, dtype, how):
         seq = PagedSequence(c["H"], c["G"], c["Dk"], c["Dv"], c["page"], T, dtype, (freq, mult, c["interleaved"]),
                             c["v_is_k"], seed=loud)
         cuts = cuts_of(T, how)
-        got = torch.cat([seq.feed(q, k, v, a, b, c["window"], c["keep"], True, 1.0, tc, 1 + (a % 3))
+        got = torch.cat([seq.feed(q, k, v, a, b, c["window"], c["keep"], True, 1.0, c.get("tc", False), 1 + (a % 3))
                          for a, b in zip(cuts[:-1], cuts[1:])])
         assert torch.isfinite(got).all()
         tol = 2e-5 if dtype == torch.float32 else 3e-2
@@ -471,6 +481,33 @@ def test_rotation_cache_and_attention_with_one_loud_key(case, dtype, how):
                                                  v if v is not None else k, 1.0, plain.visible(T, w2, k2))
             if not torch.equal(plain.visible(T, w2, k2)[:, loud], mask[:, loud]):
                 assert (other - want).abs().max() > 5 * tol * want.abs().max()
+
+
+@pytest.mark.gpu
+def test_tcgen05_prompt_kernel_shares_a_long_context_with_sink_and_kept_tiles():
+    """Behind more than a thousand keys several CTAs share a tile's key tiles, the kept ones
+    among them; the sink joins exactly one share."""
+    H, G, D, T, window, keep = 4, 2, 64, 1300, 1000, 70
+    g = torch.Generator().manual_seed(8)
+    freq, mult = plain.rotary_table("attention_2", {"base": 1000.0, "dims": 32, "scaling": {"factor": 2.0}})
+    q = (0.3 * torch.randn(T, H, D, generator=g)).to(torch.bfloat16).double()
+    k = 0.3 * torch.randn(T, G, D, generator=g)
+    u = torch.zeros(D)
+    u[32:] = 1.0 / math.sqrt(32)
+    k[3] += 6.0 * u                       # a kept key, loud
+    k[650] += 6.0 * u                     # a key deep inside the window
+    k = k.to(torch.bfloat16).double()
+    q = (q + 1.5 * u.double()).to(torch.bfloat16).double()
+    v = torch.randn(T, G, D, generator=g).to(torch.bfloat16).double()
+    pos = torch.arange(T)
+    want = plain.sink_softmax_attention(plain.rotate(q, pos, freq, mult, False), plain.rotate(k, pos, freq, mult, False),
+                                        v, 0.125, plain.visible(T, window, keep))
+    seq = PagedSequence(H, G, D, D, 16, T, torch.bfloat16, (freq, mult, False), False)
+    got = torch.cat([seq.feed(q, k, v, a, b, window, keep, True, 0.125, "tcgen05", 3)
+                     for a, b in ((0, 1200), (1200, 1300))])
+    assert torch.isfinite(got).all()
+    err = (got - want).abs().amax(dim=(1, 2))
+    assert err.max() <= 3e-2 * want.abs().max(), (int(err.argmax()), err.max().item())
 
 
 @pytest.mark.gpu

@@ -93,12 +93,26 @@ __device__ __forceinline__ void stsm_x4(uint32_t addr, const uint32_t (&r)[4]) {
                  : "memory");
 }
 
+// Options of a layer's attention beyond window and scale (X = true compiles them in; the plain
+// kernel is the X = false one). `keep_first`: with a window, keys at positions below it stay
+// visible to every later query: their key tiles come first in a CTA's list, then the window's.
+// `sink`: the softmax's denominator has one more term, a key of score 0 without a value: the
+// reference maximum and the row sum start from it (in the first of a tile's shares only).
+// `gate_mode` 2: the gate has one value per output element ([T, H * 64] rows `ldg` apart), and the
+// 32-bit output times the 32-bit sigmoid is rounded once.
+struct AtOptions {
+    int keep_first;
+    int sink;
+    int gate_mode;
+};
+
+template <bool X>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_bfloat16* out,
                        const int* positions, const int* tok_seq, const int* block_table, int bt_stride,
                        const int* tile_tok0, const int* tile_ntok, int H, int Hkv, int P, int window,
                        float scale, int p_shift, const __nv_bfloat16* gate, int64_t ldg, int max_split,
-                       float* part_o, float* part_ml, int* tickets) {
+                       float* part_o, float* part_ml, int* tickets, const AtOptions opt) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     __shared__ int s_last;
     pdl_launch_dependents();
@@ -137,11 +151,22 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
     // AT_SPLIT_TILES key tiles: CTA `split` takes key tiles split, split + nsplit, ...; the ones
     // beyond that number have nothing to do. (The launch fixes the most; the tile decides.)
     const int split = blockIdx.y;
-    const int all_tiles = (pos_last - j_begin) / AT_KEYS + 1;
+    // the kept positions that lie before the window of the tile's first row, [0, keep_end), come
+    // first in the list of key tiles
+    const int keep_first = X ? opt.keep_first : 0;
+    const int keep_end = (keep_first > 0 && lo > 0) ? min(keep_first, lo) : 0;
+    const int n_keep = (keep_end + AT_KEYS - 1) / AT_KEYS;
+    const int all_tiles = n_keep + (pos_last - j_begin) / AT_KEYS + 1;
     const int nsplit = min(max_split, max(1, all_tiles / AT_SPLIT_TILES));
     if (split >= nsplit) return;
     const int n_tiles = (all_tiles - split + nsplit - 1) / nsplit;       // at least one
-    auto tile_j0 = [&](int it) { return j_begin + (split + it * nsplit) * AT_KEYS; };
+    // key tile `it` of this CTA: its first key, and the first and last key it may read
+    auto tile_j0 = [&](int it) {
+        const int t = split + it * nsplit;
+        return t < n_keep ? t * AT_KEYS : j_begin + (t - n_keep) * AT_KEYS;
+    };
+    auto tile_lo = [&](int it) { return split + it * nsplit < n_keep ? 0 : lo; };
+    auto tile_hi = [&](int it) { return split + it * nsplit < n_keep ? keep_end - 1 : pos_last; };
 
     if (tid == 0) {
         for (int i = 0; i < AT_STAGES; ++i) {
@@ -196,15 +221,15 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             const int j0 = tile_j0(it);
             const uint32_t kt = k_tile0 + (uint32_t)s * AT_KV_BYTES, vs = v_stage;
             if (p_shift >= 0) {
-                loader.issue_looked_up(kt, vs, pool, j0, lo, pos_last);
-                if (it + 1 < n_tiles) loader.lookup(bt_row, tile_j0(it + 1), lo, pos_last);
+                loader.issue_looked_up(kt, vs, pool, j0, tile_lo(it), tile_hi(it));
+                if (it + 1 < n_tiles) loader.lookup(bt_row, tile_j0(it + 1), tile_lo(it + 1), tile_hi(it + 1));
             } else {
-                load_tile<AT_D>(kt, pool, bt_row, j0, AT_KEYS, lo, pos_last, kvh, Hkv, P, 0, tid, 128);
-                load_tile<AT_D>(vs, pool, bt_row, j0, AT_KEYS, lo, pos_last, kvh, Hkv, P, 1, tid, 128);
+                load_tile<AT_D>(kt, pool, bt_row, j0, AT_KEYS, tile_lo(it), tile_hi(it), kvh, Hkv, P, 0, tid, 128);
+                load_tile<AT_D>(vs, pool, bt_row, j0, AT_KEYS, tile_lo(it), tile_hi(it), kvh, Hkv, P, 1, tid, 128);
             }
             cp_async_commit();
         };
-        if (p_shift >= 0 && n_tiles > 0) loader.lookup(bt_row, tile_j0(0), lo, pos_last);
+        if (p_shift >= 0 && n_tiles > 0) loader.lookup(bt_row, tile_j0(0), tile_lo(0), tile_hi(0));
         if (n_tiles > 0) issue(0);
         // (after a failed wait the loop still runs to its end, without waiting: every thread must
         // meet every named barrier)
@@ -280,6 +305,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
         const float scale_log2 = scale * LOG2E;
         float m_ref = -INFINITY;
         float2 l_run = make_float2(0.f, 0.f), l_alt = make_float2(0.f, 0.f);   // the row sum in four lanes
+        if (X && opt.sink && split == 0) {
+            m_ref = 0.f;
+            l_run.x = 1.f;
+        }
         bool ok = true;
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1, j0 = tile_j0(j);
@@ -297,8 +326,16 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             __syncwarp();
             if (lane == 0) mbar_arrive(s_free(b));
             // a tile every row of the CTA sees whole needs no comparisons
+            const bool kept = X && split + j * nsplit < n_keep;
             const bool masked = j0 + AT_KEYS - 1 > pos_first || (window > 0 && j0 < pos_last - window + 1) ||
-                                rows < AT_ROWS;
+                                rows < AT_ROWS || kept;
+            // what this row sees of the tile: [see_lo, see_hi], and below keep_first whatever the window
+            const int see_hi = X ? min(pos_r, tile_hi(j)) : pos_r;
+            const int see_lo = X ? tile_lo(j) : 0;
+            auto sees = [&](int key) {
+                if constexpr (X) return key <= see_hi && key >= see_lo && (key >= lo_r || key < keep_first);
+                else return key <= pos_r && key >= lo_r;
+            };
             // the row's maximum over the tile's visible keys (the scale is positive)
             // (four chains: a thread has few other warps to hide a 64-deep dependency behind)
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -306,8 +343,8 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                     const int key = j0 + e;
-                    if (key <= pos_r && key >= lo_r) mx4[e & 1] = fmaxf(mx4[e & 1], s_lo[e]);
-                    if (key + 32 <= pos_r && key + 32 >= lo_r) mx4[2 + (e & 1)] = fmaxf(mx4[2 + (e & 1)], s_hi[e]);
+                    if (sees(key)) mx4[e & 1] = fmaxf(mx4[e & 1], s_lo[e]);
+                    if (sees(key + 32)) mx4[2 + (e & 1)] = fmaxf(mx4[2 + (e & 1)], s_hi[e]);
                 }
             } else {
 #pragma unroll
@@ -317,6 +354,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             const bool raise = __any_sync(0xffffffffu, mx > m_ref + AT_LAZY);
             if (raise) {
                 const float m_new = fmaxf(m_ref, mx);
+                if (X && j == 0) {            // nothing accumulated yet but, with a sink, the sum's first term
+                    const float alpha0 = m_new == -INFINITY ? 1.0f : fast_exp2(m_ref - m_new);
+                    l_run.x *= alpha0;
+                }
                 if (j >= 1) {
                     // the product of the tile before must have landed before the output is touched
                     if (ok) ok = at_wait(pv_full, (uint32_t)((j - 1) & 1), 7);
@@ -350,8 +391,8 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
                     for (int e = 0; e < 32; e += 2) {
                         float p0 = 0.f, p1 = 0.f;
                         const int key = j0 + c + e;
-                        if (key <= pos_r && key >= lo_r) p0 = fast_exp2(fmaf(part[e], scale_log2, neg_m));
-                        if (key + 1 <= pos_r && key + 1 >= lo_r) p1 = fast_exp2(fmaf(part[e + 1], scale_log2, neg_m));
+                        if (sees(key)) p0 = fast_exp2(fmaf(part[e], scale_log2, neg_m));
+                        if (sees(key + 1)) p1 = fast_exp2(fmaf(part[e + 1], scale_log2, neg_m));
                         if (e & 2) l_alt = add2(l_alt, make_float2(p0, p1));
                         else l_run = add2(l_run, make_float2(p0, p1));
                         packed[e >> 1] = pack_bf16_pair(p0, p1);
@@ -392,7 +433,11 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             __nv_bfloat16* dst = r < rows ? out + ((size_t)(tok0 + r / G) * H + kvh * G + r % G) * AT_D : nullptr;
             // the per-head output gate, if the layer has one: round(round(o) * round(sigmoid(g)))
             float gs = 1.0f;
-            if (gate != nullptr && dst != nullptr) {
+            const bool by_element = X && opt.gate_mode == 2;
+            const __nv_bfloat16* grow = by_element && dst != nullptr
+                                            ? gate + (size_t)(tok0 + r / G) * ldg + (size_t)(kvh * G + r % G) * AT_D
+                                            : nullptr;
+            if (gate != nullptr && dst != nullptr && !by_element) {
                 const float gv = __bfloat162float(gate[(size_t)(tok0 + r / G) * ldg + kvh * G + r % G]);
                 gs = round_as<__nv_bfloat16>(1.0f / (1.0f + expf(-gv)));
             }
@@ -400,6 +445,19 @@ attn_prefill_tc_kernel(const __nv_bfloat16* q, const __nv_bfloat16* pool, __nv_b
             auto store16 = [&](int c, const float (&part)[16], float inv) {
                 if (dst == nullptr) return;
                 uint32_t packed[8];
+                if (by_element) {
+                    const uint4 g0 = *reinterpret_cast<const uint4*>(grow + c), g1 = *reinterpret_cast<const uint4*>(grow + c + 8);
+                    const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+                    for (int e = 0; e < 16; e += 2) {
+                        const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[e >> 1]));
+                        packed[e >> 1] = pack_bf16_pair(part[e] * inv / (1.0f + __expf(-gv.x)),
+                                                        part[e + 1] * inv / (1.0f + __expf(-gv.y)));
+                    }
+                    *reinterpret_cast<uint4*>(dst + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    return;
+                }
 #pragma unroll
                 for (int e = 0; e < 16; e += 2) {
                     packed[e >> 1] = pack_bf16_pair(part[e] * inv, part[e + 1] * inv);
@@ -515,11 +573,21 @@ TK_API int tk_attn_prefill_tc_status() {
 // each tile takes as many as leave a CTA 8 key tiles), for steps with few tiles and long
 // contexts, where one CTA per tile would walk its keys alone on an idle GPU; `scratch`: tk_attn_prefill_tc_scratch floats, `tickets`: n_tiles * Hkv ints that are
 // zero and are zero again afterwards (the last CTA of a tile to finish merges the shares).
-TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, const int* positions,
-                              const int* tok_seq, const int* block_table, int bt_stride,
-                              const int* tile_tok0, const int* tile_ntok, int n_tiles, int H, int Hkv, int D,
-                              int P, int window, float scale, const void* gate, int64_t ldg, int nsplit,
-                              float* scratch, int* tickets, cudaStream_t stream) {
+// keep_first, sink, gate_mode: see AtOptions (all zero, or gate_mode 1 with a gate: the plain kernel).
+TK_API int tk_attn_prefill_tc_opt(const void* q, const void* kv_pool, void* out, const int* positions,
+                                  const int* tok_seq, const int* block_table, int bt_stride,
+                                  const int* tile_tok0, const int* tile_ntok, int n_tiles, int H, int Hkv, int D,
+                                  int P, int window, float scale, const void* gate, int64_t ldg, int nsplit,
+                                  float* scratch, int* tickets, int keep_first, int sink, int gate_mode,
+                                  cudaStream_t stream) {
+    TK_CHECK_ARG(keep_first >= 0 && (keep_first == 0 || window > 0), "attn_prefill_tc: kept first positions need a window");
+    TK_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0) == (gate == nullptr),
+                 "attn_prefill_tc: gate mode %d and the gate do not go together", gate_mode);
+    TK_CHECK_ARG(gate_mode != 2 || (ldg % 8 == 0 && (uintptr_t)gate % 16 == 0),
+                 "attn_prefill_tc: a gate per element is read 16 bytes at a time: rows a multiple of 8 elements "
+                 "apart, 16-byte aligned");
+    const AtOptions opt{keep_first, sink ? 1 : 0, gate_mode};
+    const bool x = keep_first > 0 || sink || gate_mode == 2;
     TK_CHECK_ARG(tk_attn_prefill_tc_supported(H, Hkv, D), "attn_prefill_tc: shape H=%d Hkv=%d D=%d is not taken "
                  "(head size 64, a group that divides 128)", H, Hkv, D);
     TK_CHECK_ARG(P > 0 && n_tiles >= 0, "attn_prefill_tc: bad page size or tile count");
@@ -534,16 +602,28 @@ TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, con
         while ((1 << shift) < P) ++shift;
     }
     const size_t smem = 1024 + AT_Q_BYTES + (2 * AT_STAGES + 1) * AT_KV_BYTES + 2 * AT_P_BYTES + (2 * AT_STAGES + 8) * 8 + 64;
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(x ? attn_prefill_tc_kernel<true> : attn_prefill_tc_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
-        e = tk_launch(attn_prefill_tc_kernel, dim3(n_tiles * Hkv, nsplit), dim3(AT_THREADS), smem, stream,
+        e = tk_launch(x ? attn_prefill_tc_kernel<true> : attn_prefill_tc_kernel<false>, dim3(n_tiles * Hkv, nsplit),
+                      dim3(AT_THREADS), smem, stream,
                       (const __nv_bfloat16*)q, (const __nv_bfloat16*)kv_pool, (__nv_bfloat16*)out, positions, tok_seq,
                       block_table, bt_stride, tile_tok0, tile_ntok, H, Hkv, P, window, scale, shift,
-                      (const __nv_bfloat16*)gate, ldg, nsplit, part_o, part_ml, tickets);
+                      (const __nv_bfloat16*)gate, ldg, nsplit, part_o, part_ml, tickets, opt);
     if (e != cudaSuccess) {
         tk_set_error("attn_prefill_tc: launch failed: %s", cudaGetErrorString(e));
         cudaGetLastError();
         return -2;
     }
     return 0;
+}
+
+TK_API int tk_attn_prefill_tc(const void* q, const void* kv_pool, void* out, const int* positions,
+                              const int* tok_seq, const int* block_table, int bt_stride,
+                              const int* tile_tok0, const int* tile_ntok, int n_tiles, int H, int Hkv, int D,
+                              int P, int window, float scale, const void* gate, int64_t ldg, int nsplit,
+                              float* scratch, int* tickets, cudaStream_t stream) {
+    return tk_attn_prefill_tc_opt(q, kv_pool, out, positions, tok_seq, block_table, bt_stride, tile_tok0, tile_ntok,
+                                  n_tiles, H, Hkv, D, P, window, scale, gate, ldg, nsplit, scratch, tickets, 0, 0,
+                                  gate != nullptr ? 1 : 0, stream);
 }

@@ -48,9 +48,9 @@ class Attention:
             raise ValueError("attention: kept first positions need a window")
         self.sink, self.keep_first, self.v_dim, self.v_is_k = bool(sink), int(keep_first), v_dim, bool(v_is_k)
         self.gate_kind, self.exact = gate_kind, bool(exact)
-        # what the one-kernel decode form, the tcgen05 prefill kernel and the norms folded into
-        # the projections do not take (the mma.sync kernels take all of it but a value size of
-        # its own; the general kernel takes everything)
+        # what the one-kernel decode form and the norms folded into the projections do not take
+        # (the tensor-core kernels take all of it but a value size of its own; the general
+        # kernel takes everything)
         self.extended = bool(self.sink or self.keep_first or self.v_is_k or v_dim != head_dim
                              or gate_kind != "head" or self.exact)
         if heads % kv_heads:
@@ -242,18 +242,18 @@ class Attention:
         out = torch.empty_like(q)
         # prompt portions: the tcgen05 kernel (tiles of 128 rows) where it takes the shape, else
         # the mma.sync one (tiles of 64 rows)
-        # (the tcgen05 kernel is the plain form's: a sink, kept positions or a gate per element
-        # go to the mma.sync kernel)
-        tc = (self.prefill_tc and not (self.sink or self.keep_first or self.gate_kind != "head")
-              and ops.attention_prefill_tc_supported(self.heads, self.kv_heads, self.head_dim, q.dtype))
+        tc = self.prefill_tc and ops.attention_prefill_tc_supported(self.heads, self.kv_heads, self.head_dim,
+                                                                     q.dtype)
         by_element = self.gate_kind == "element"
+        if by_element and gate is not None and (gate.stride(0) % 8 or gate.data_ptr() % 16):
+            tc = False               # the tcgen05 kernel reads such a gate 16 bytes at a time
         per_tile = (ops.attention_prefill_tc_tokens if tc else ops.attention_prefill_mma_tokens)(
             self.heads, self.kv_heads)
         _, tok0, _, ntok = ctx.tiles(per_tile, "multi")
         if tok0.numel() and tc:
             nsplit = self.prefill_splits(ctx.n_tokens, tok0.numel(), per_tile, self.kv_heads, self.tuning)
             ops.attention_prefill_tc(q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window,
-                                     self.scale, gate, nsplit)
+                                     self.scale, gate, nsplit, self.keep_first, self.sink, by_element)
         elif tok0.numel():
             ops.attention_prefill_mma(q, pool, out, ctx.positions, ctx.tok_seq, table, tok0, ntok, self.window,
                                       self.scale, gate, self.keep_first, self.sink, by_element)
