@@ -1005,23 +1005,21 @@ def design_kernels(z: dict, pk: dict) -> list[dict]:
     ntok = torch.full_like(tok0, per)
     visible = sum(min(i + 1, win) for i in range(T))
     flops = 4.0 * visible * H * D
-    ours = _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, table, tok0, ntok, win, D ** -0.5,
-                                                       gate_e, 4, True, True), flush)
+    # both designs take the tcgen05 kernel at head size 64 and the mma.sync kernel at 128
     if ops.attention_prefill_tc_supported(H, G, D, bf):
         per_tc = ops.attention_prefill_tc_tokens(H, G)
         tok0_tc = torch.arange(0, T, per_tc, dtype=torch.int32, device=dev)
         ntok_tc = torch.full_like(tok0_tc, per_tc)
-        theirs = _timed_us(lambda: ops.attention_prefill_tc(q, pool, out, pos, seq, table, tok0_tc, ntok_tc, win,
-                                                            D ** -0.5, gate_h, 1), flush)
-        like = "tcgen05"
-    else:
-        theirs = _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, table, tok0, ntok, win,
-                                                             D ** -0.5, gate_h), flush)
-        like = "mma.sync"
-    add(f"prompt attention (LFM3: {like})", ours, theirs, flops, flops, "flops")
-    plain = _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, table, tok0, ntok, win, D ** -0.5,
-                                                        gate_h), flush)
-    add("prompt attention (LFM3: mma.sync)", ours, plain, flops, flops, "flops")
+        add("prompt attention (tcgen05)",
+            _timed_us(lambda: ops.attention_prefill_tc(q, pool, out, pos, seq, table, tok0_tc, ntok_tc, win,
+                                                       D ** -0.5, gate_e, 1, 4, True, True), flush),
+            _timed_us(lambda: ops.attention_prefill_tc(q, pool, out, pos, seq, table, tok0_tc, ntok_tc, win,
+                                                       D ** -0.5, gate_h, 1), flush), flops, flops, "flops")
+    add("prompt attention (mma.sync)",
+        _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, table, tok0, ntok, win, D ** -0.5,
+                                                    gate_e, 4, True, True), flush),
+        _timed_us(lambda: ops.attention_prefill_mma(q, pool, out, pos, seq, table, tok0, ntok, win, D ** -0.5,
+                                                    gate_h), flush), flops, flops, "flops")
     # decode: B sequences of T cached positions each (they share the pages: the bytes are read per sequence)
     B = 64
     dpos = torch.full((B,), T - 1, dtype=torch.int32, device=dev)

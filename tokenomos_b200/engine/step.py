@@ -158,7 +158,8 @@ class _DecodeGraph:
         self.host = [torch.zeros(self.size, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.host_np = [h.numpy() for h in self.host]
         # what each staging buffer's block-table rows hold: (request, entries written) per row
-        self.host_rows = [{g: [(None, 0, 0)] * b for g in self.groups} for _ in range(self.RING)]
+        # (request, its life, entries written, blocks a window had given back by then) per row
+        self.host_rows = [{g: [(None, 0, 0, 0)] * b for g in self.groups} for _ in range(self.RING)]
         self.tokens_host = [torch.zeros(b, dtype=torch.int32).pin_memory() for _ in range(self.RING)]
         self.turn = 0
         self.dev = torch.zeros(self.size, dtype=torch.int32, device=dev)
@@ -624,29 +625,36 @@ class StepFunction:
         o, _ = g.off["sampling"]
         sampler.pack_rows_into(h[o:o + 6 * b], sampling_rows, b)
         # block tables: a row that held the same request the last time this staging buffer was
-        # used only gets its new entries (a window group's entries also turn to 0: rewritten)
+        # used only gets its new entries, and zeros where a window has given pages back since
         for grp in g.groups:
             o, _ = g.off[("table", grp)]
             held = rows_held[grp]
-            incremental = cache.groups[grp].window is None
+            group = cache.groups[grp]
+            windowed = group.window is not None
+            kept = -(-group.keep_first // cache.page_size)       # blocks a window never gives back
             for i, (rid, st) in enumerate(zip(rids, states)):
                 row = st.tables[grp]
                 have = len(row)
-                held_rid, held_epoch, held_len = held[i]
-                if incremental and held_len <= have and held_rid == rid and held_epoch == st.epoch:
-                    if held_len == have:
+                live = st.first_live.get(grp, 0) if windowed else 0
+                held_rid, held_epoch, held_len, held_live = held[i]
+                if held_len <= have and held_live <= live and held_rid == rid and held_epoch == st.epoch:
+                    if held_len == have and held_live == live:
                         continue                 # the common case: the same pages as last time
                     base = o + i * width
-                    h[base + held_len:base + have] = row[held_len:]
+                    if held_len < have:
+                        h[base + held_len:base + have] = row[held_len:]
+                    first = max(held_live, kept)
+                    if first < live:
+                        h[base + first:base + live] = 0
                 else:
                     base = o + i * width
                     h[base:base + have] = row
                     h[base + have:base + width] = 0
-                held[i] = (rid, st.epoch, have)
+                held[i] = (rid, st.epoch, have, live)
             for i in range(n, b):
                 if held[i][0] is not None:
                     h[o + i * width:o + (i + 1) * width] = 0
-                    held[i] = (None, 0, 0)
+                    held[i] = (None, 0, 0, 0)
         g.dev.copy_(g.host[turn], non_blocking=True)
         g.graph.replay()
         g.tokens_host[turn].copy_(g.tokens, non_blocking=True)
