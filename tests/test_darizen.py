@@ -74,11 +74,20 @@ DZ_D = {"architecture": "Darizen", "vocab": 400, "width": 128, "norm": {"eps": 1
                    dict(att(8, 2, 64, 70), mlp=None)],
         "loop": {"start": 1, "stop": 3, "times": 3}}
 
+# E: sizes no 16-byte kernel takes: a width that is no multiple of 8, head and value sizes of 10
+#    and 6, an odd feed-forward size; the loop is the last layer
+DZ_E = {"architecture": "Darizen", "vocab": 50, "width": 36, "norm": {"eps": 1e-5},
+        "layers": [dict(att2(3, 3, 10, 6, 7, keep_first=2, dims=6, factor=3.0), mlp=mlp(30, 1.0)),
+                   dict(att(2, 1, 12, 5, scaling={"factor": 2.0, "original": 16, "fast": 8.0, "slow": 1.0}),
+                        mlp=mlp(21, 2.0))],
+        "loop": {"start": 1, "stop": 2, "times": 2}}
+
 CASES = {
     "A": dict(config=DZ_A, seed=11, page=4, lengths=[1, 2, 7, 30, 61, 45]),
     "B": dict(config=DZ_B, seed=12, page=8, lengths=[3, 19, 21, 50, 90, 33]),
     "C": dict(config=DZ_C, seed=13, page=16, lengths=[1, 5, 64, 65, 140]),
     "D": dict(config=DZ_D, seed=14, page=16, lengths=[2, 31, 150, 65, 200, 90]),
+    "E": dict(config=DZ_E, seed=15, page=4, lengths=[1, 6, 23, 40]),
 }
 # Bounds relative to the request's largest |logit|, about twice what a B200 measured. Against
 # the float64 plain implementation, 32-bit: A 2.2e-6, B 1.9e-6, C 1.7e-6, D 1.4e-5 (D runs its
@@ -89,12 +98,13 @@ CASES = {
 # 16 bits first, and the tensor-core attention (D) rounds the softmax's weights against other
 # running maxima in its prompt and decode forms. Their difference is that of two roundings of the
 # same values and is held to about the bound each has against the plain implementation
-# (measured: A 1.2 %, B 1.1 %, C 0.54 %, D 4.2 %); the 32-bit path, where the cut changes no
+# (measured: A 1.2 %, B 1.1 %, C 0.54 %, D 4.2 %; E, whose sizes only the scalar kernels take,
+# 1.8 % against the plain implementation and not a bit between cuts); the 32-bit path, where the cut changes no
 # rounding, is what holds the cache and the batch to 2e-5.
-TOL_F32 = {"A": 1e-5, "B": 1e-5, "C": 1e-5, "D": 4e-5}
-TOL_F32_SAME = {"A": 5e-6, "B": 5e-6, "C": 2e-6, "D": 2e-5}
-TOL_BF16 = {"A": 4.5e-2, "B": 4.5e-2, "C": 6e-2, "D": 0.2}
-TOL_BF16_SAME = {"A": 2.5e-2, "B": 2.5e-2, "C": 1.2e-2, "D": 8e-2}
+TOL_F32 = {"A": 1e-5, "B": 1e-5, "C": 1e-5, "D": 4e-5, "E": 1e-5}
+TOL_F32_SAME = {"A": 5e-6, "B": 5e-6, "C": 2e-6, "D": 2e-5, "E": 5e-6}
+TOL_BF16 = {"A": 4.5e-2, "B": 4.5e-2, "C": 6e-2, "D": 0.2, "E": 4e-2}
+TOL_BF16_SAME = {"A": 2.5e-2, "B": 2.5e-2, "C": 1.2e-2, "D": 8e-2, "E": 5e-3}
 
 
 def make_tensors(config: dict, seed: int) -> dict[str, torch.Tensor]:
@@ -545,7 +555,7 @@ def oracle(name, folders, reqs):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_every_way_of_cutting(name, dtype, folders):
     folder, _ = folders[name]
     page = CASES[name]["page"]
