@@ -578,6 +578,63 @@ def test_every_way_of_cutting(name, dtype, folders):
                 f"{name} {dtype} {mode} vs whole")
 
 
+def random_config(seed: int) -> tuple[dict, int]:
+    """A configuration drawn from everything the design lets vary, and a page size."""
+    import random
+
+    rng = random.Random(seed)
+    width = rng.choice([32, 40, 64, 96])
+    layers = []
+    for _ in range(rng.randint(1, 4)):
+        heads = rng.choice([1, 2, 3, 4, 6, 8])
+        kv_heads = rng.choice([g for g in (1, 2, 3, 4, 6, 8) if heads % g == 0])
+        dim = rng.choice([8, 12, 16, 24, 32, 64, 64])
+        dims = rng.choice([dim, dim, 2, dim // 2 - (dim // 2) % 2 or 2])
+        window = rng.choice([1, 2, 5, 16, 33, 100])
+        scale = rng.choice([dim ** -0.5, 0.05, 0.3])
+        base = rng.choice([100.0, 10000.0, 500000.0])
+        if rng.random() < 0.5:
+            scaling = rng.choice([None, {"factor": rng.choice([2.0, 8.0]), "original": rng.choice([16, 64, 2048]),
+                                         "fast": rng.choice([8.0, 32.0]), "slow": rng.choice([1.0, 2.0])}])
+            layer = att(heads, kv_heads, dim, window, dims=dims, scaling=scaling, base=base, scale=scale)
+        else:
+            vdim = rng.choice([dim, dim, 8, 12, 20])
+            layer = att2(heads, kv_heads, dim, vdim, window, keep_first=rng.choice([None, 0, 1, 3, 9, 40]), dims=dims,
+                         factor=rng.choice([None, 2.0, 8.0]), base=base, scale=scale)
+        layer["mlp"] = None if rng.random() < 0.2 else mlp(rng.choice([16, 24, 30, 64]), rng.choice([0.5, 1.5, 7.0]))
+        layers.append(layer)
+    config = {"architecture": "Darizen", "vocab": rng.randint(40, 300), "width": width,
+              "norm": {"eps": rng.choice([1e-5, 1e-6])}, "layers": layers}
+    if rng.random() < 0.7:
+        start = rng.randrange(len(layers))
+        config["loop"] = {"start": start, "stop": rng.randint(start + 1, len(layers)), "times": rng.randint(1, 3)}
+    return config, rng.choice([4, 8, 16])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("seed", range(24))
+def test_random_configurations(seed, tmp_path):
+    """Configurations nobody chose: whatever sizes, layer order, windows, kept ranges, loops and
+    constants the draw gives, the 32-bit model meets the plain implementation however the
+    requests are cut, and the 16-bit one stays close to it."""
+    from safetensors.torch import save_file
+
+    config, page = random_config(seed)
+    tensors = make_tensors(config, 100 + seed)
+    (tmp_path / "config.json").write_text(json.dumps(config))
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(tmp_path / "model.safetensors"))
+    w = {k: v.double() for k, v in tensors.items()}
+    g = torch.Generator().manual_seed(seed)
+    reqs = {f"r{i}": torch.randint(0, config["vocab"], (n,), generator=g).tolist()
+            for i, n in enumerate([1, 2, 17, 45, 80, 130])}
+    want = {rid: plain.forward(config, w, ids)[0] for rid, ids in reqs.items()}
+    for dtype, tol in (("float32", 5e-5), ("bfloat16", 0.25)):
+        for steps in (trace_util.portions(reqs), trace_util.mixed(reqs, live=4, seed=seed)):
+            per_step = trace_util.run_in_process(tmp_path, dtype, steps, trace_util.max_live_tokens(steps, page), page,
+                                                 max_requests=4)
+            compare(trace_util.collect(steps, per_step), want, tol, f"random configuration {seed} {dtype}: {config}")
+
+
 @pytest.mark.gpu
 def test_layer_runs_one_by_one(folders):
     """The residual stream after every layer run, in 32-bit: a fault shows at the run that has it."""
