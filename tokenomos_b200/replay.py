@@ -68,6 +68,8 @@ def main(argv: list[str] | None = None) -> int:
             rid = e["id"]
             if rid not in cache.requests:
                 cache.admit(rid)
+            if not e.get("tokens"):
+                continue                     # admitted, but nothing of it runs in this step
             entries.append(StepEntry(rid, [int(t) for t in e["tokens"]],
                                      [int(w) for w in e.get("want", [])]))
         if entries:
