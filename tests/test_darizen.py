@@ -381,6 +381,12 @@ class PagedSequence:
         positions = torch.arange(a, b, dtype=torch.int32, device="cuda")
         seq = torch.zeros(n, dtype=torch.int32, device="cuda")
         freq, mult, interleaved = self.rotary
+        if tensor_cores == "fused" and n == 1:
+            # the one-kernel decode form: rotation, cache write, split attention and merge
+            return ops.attention_decode_fused(rows, self.pool, None, None, 0.0, dev(freq), None, positions, seq,
+                                              self.table, self.H, self.G, window, scale, nsplit, general=True,
+                                              cs_mult=mult, interleaved=interleaved, v_is_k=self.v_is_k,
+                                              keep_first=keep_first, sink=sink).cpu().double()
         qr = ops.rotary_write(rows, self.pool, dev(freq), mult, positions, seq, self.table, self.H, self.G,
                               self.Dk, self.Dv, self.P, interleaved, self.v_is_k)
         if tensor_cores:
@@ -433,6 +439,10 @@ def cuts_of(T: int, how: str) -> list[int]:
     dict(H=8, G=2, Dk=64, Dv=64, page=16, window=40, keep=5, interleaved=False, v_is_k=False, dims=32, tc=True),
     dict(H=4, G=2, Dk=128, Dv=128, page=16, window=24, keep=0, interleaved=True, v_is_k=True, dims=64, tc=True),
     dict(H=4, G=1, Dk=64, Dv=64, page=8, window=70, keep=66, interleaved=False, v_is_k=False, dims=16, tc=True),
+    # decoded tokens through the one-kernel form (rotation and cache write inside), both pairings
+    dict(H=8, G=2, Dk=64, Dv=64, page=16, window=40, keep=5, interleaved=False, v_is_k=False, dims=32, tc="fused"),
+    dict(H=4, G=2, Dk=128, Dv=128, page=16, window=24, keep=0, interleaved=True, v_is_k=True, dims=64, tc="fused"),
+    dict(H=4, G=1, Dk=64, Dv=64, page=8, window=70, keep=66, interleaved=True, v_is_k=True, dims=16, tc="fused"),
     # the tcgen05 prompt kernel (head size 64), whole tiles of 128 rows and ragged ones, keys shared by several CTAs
     dict(H=8, G=2, Dk=64, Dv=64, page=16, window=40, keep=5, interleaved=False, v_is_k=False, dims=32, tc="tcgen05"),
     dict(H=4, G=4, Dk=64, Dv=64, page=16, window=150, keep=70, interleaved=True, v_is_k=True, dims=32, tc="tcgen05"),

@@ -596,9 +596,15 @@ struct DecodeFused {
     int* tickets;
     int p_shift;
     int write_kv;                   // 0: the layer reads another layer's cache, which holds this step's key already
+    // the general form (the kernel's X = true instantiation): cos and sin times cs_mult and not
+    // rounded; column pairs (2i, 2i + 1) instead of (i, i + R/2); the value is the key as projected
+    // (qkv holds no value heads); and the options of AttnOptions
+    float cs_mult;
+    int interleaved, v_is_k;
+    AttnOptions opt;
 };
 
-template <int D>
+template <int D, bool X = false>
 __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFused a) {
     pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -621,11 +627,24 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
     const int g = lane >> 2, t = lane & 3;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int j_begin = (lo / 32) * 32;
-    const int tiles = (pos - j_begin) / 32 + 1;
+    // the key tiles: first those of the kept positions before the window, [0, keep_end), then
+    // from the window's start to the token's own position
+    const int keep_first = X ? a.opt.keep_first : 0;
+    const int keep_end = (keep_first > 0 && lo > 0) ? min(keep_first, lo) : 0;
+    const int n_keep = (keep_end + 31) / 32;
+    const int tiles = n_keep + (pos - j_begin) / 32 + 1;
     const int per_split = (tiles + nsplit - 1) / nsplit;
     const int t_begin = split * per_split, t_end = min(tiles, t_begin + per_split);
     const int last_tile = tiles - 1;                         // the tile that holds position `pos`
     const int j_last = a.write_kv ? pos - 1 : pos;           // the last key that comes from the cache
+    // a tile's first key, and the first and last key that its copies may read
+    auto range = [&](int tile, int& j0, int& j_lo, int& j_hi) {
+        if (tile < n_keep) {
+            j0 = tile * 32, j_lo = 0, j_hi = keep_end - 1;
+        } else {
+            j0 = j_begin + (tile - n_keep) * 32, j_lo = lo, j_hi = j_last;
+        }
+    };
     const bool owner = a.write_kv && t_begin <= last_tile && last_tile < t_end;
     size_t cache_row = 0;
     if (owner) {
@@ -636,30 +655,37 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
     for (int k = tid; k < half; k += 128) {
         float s_, c_;
         sincosf((float)pos * a.inv_freq[k], &s_, &c_);
-        sm_cs[k] = round_as<__nv_bfloat16>(c_);
-        sm_sn[k] = round_as<__nv_bfloat16>(s_);
+        sm_cs[k] = X ? c_ * a.cs_mult : round_as<__nv_bfloat16>(c_);
+        sm_sn[k] = X ? s_ * a.cs_mult : round_as<__nv_bfloat16>(s_);
     }
 
     // the warp's private double buffer: [stage][K|V][32][D]
     const uint32_t wbase = smem_u32(smem_raw) + (uint32_t)warp * 4 * TILE_BYTES;
     PagedLoader<D, 32, 32> loader;
     loader.init(lane, kvh, Hkv, P, a.p_shift);
+    // (the page lookups clamp to positions that are held: up to `pos`, whose page this step holds)
+    auto look = [&](int tile) {
+        int j0, j_lo, j_hi;
+        range(tile, j0, j_lo, j_hi);
+        loader.lookup(bt_row, j0, j_lo, tile < n_keep ? j_hi : pos);
+    };
     auto issue = [&](int tile, int stage) {
         const uint32_t base = wbase + (uint32_t)stage * 2 * TILE_BYTES;
-        const int j0 = j_begin + tile * 32;
+        int j0, j_lo, j_hi;
+        range(tile, j0, j_lo, j_hi);
         if (a.p_shift >= 0) {
-            loader.issue_looked_up(base, base + TILE_BYTES, a.pool, j0, lo, j_last);
-            if (tile + 4 < t_end) loader.lookup(bt_row, j0 + 4 * 32, lo, pos);
+            loader.issue_looked_up(base, base + TILE_BYTES, a.pool, j0, j_lo, j_hi);
+            if (tile + 4 < t_end) look(tile + 4);
         } else {
-            load_tile<D>(base, a.pool, bt_row, j0, 32, lo, j_last, kvh, Hkv, P, 0, lane, 32);
-            load_tile<D>(base + TILE_BYTES, a.pool, bt_row, j0, 32, lo, j_last, kvh, Hkv, P, 1, lane, 32);
+            load_tile<D>(base, a.pool, bt_row, j0, 32, j_lo, j_hi, kvh, Hkv, P, 0, lane, 32);
+            load_tile<D>(base + TILE_BYTES, a.pool, bt_row, j0, 32, j_lo, j_hi, kvh, Hkv, P, 1, lane, 32);
         }
         cp_async_commit();
     };
     const int first = t_begin + warp;
     const bool deferred = first == last_tile;                // this step writes into that tile
     if (first < t_end && !deferred) {
-        if (a.p_shift >= 0) loader.lookup(bt_row, j_begin + first * 32, lo, pos);
+        if (a.p_shift >= 0) look(first);
         issue(first, 0);
     }
     pdl_wait();
@@ -669,7 +695,8 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
     {
         constexpr int LPH = D / 8, HPP = 32 / LPH;
         const int sub = lane / LPH, c = (lane % LPH) * 8;
-        const int jobs = G + (a.write_kv ? 2 : 0);
+        const bool v_is_k = X && a.v_is_k;
+        const int jobs = G + (a.write_kv ? (v_is_k ? 1 : 2) : 0);
         const int half_lanes = half / 8;
         const int partner = c < half ? lane + half_lanes : (c < a.R ? lane - half_lanes : lane);
         const __nv_bfloat16* row = a.qkv + (size_t)tok * a.ldq;
@@ -711,7 +738,18 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
             for (int k = 0; k < 8; ++k) pv[k] = __shfl_sync(0xffffffffu, v[k], partner);
             if (!live) continue;
             uint4 packed = raw;
-            if (rotate) {
+            if (X && rotate && a.interleaved) {
+                // pairs (2i, 2i + 1): both columns are this lane's
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
+                if (c < a.R) {
+                    const int i0 = c >> 1;
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        o[2 * p] = __float2bfloat16_rn(v[2 * p] * sm_cs[i0 + p] - v[2 * p + 1] * sm_sn[i0 + p]);
+                        o[2 * p + 1] = __float2bfloat16_rn(v[2 * p + 1] * sm_cs[i0 + p] + v[2 * p] * sm_sn[i0 + p]);
+                    }
+                }
+            } else if (rotate) {
                 __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(&packed);
                 const int i0 = c < half ? c : c - half;
 #pragma unroll
@@ -723,6 +761,14 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
             }
             if (job < G) {
                 *reinterpret_cast<uint4*>(sm_q + job * QS + c) = packed;
+            } else if (v_is_k) {
+                // the rotated key, and as its value the key as it was projected
+                *reinterpret_cast<uint4*>(sm_new + c) = packed;
+                *reinterpret_cast<uint4*>(sm_new + D + c) = raw;
+                if (owner) {
+                    *reinterpret_cast<uint4*>(a.pool + (cache_row + (size_t)kvh * P) * D + c) = packed;
+                    *reinterpret_cast<uint4*>(a.pool + (cache_row + (size_t)(Hkv + kvh) * P) * D + c) = raw;
+                }
             } else {
                 *reinterpret_cast<uint4*>(sm_new + (job - G) * D + c) = packed;
                 if (owner)
@@ -749,6 +795,10 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
     }
     const int pos_lo = g < G ? pos : -1, pos_hi = g + 8 < G ? pos : -1;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (X && a.opt.sink && split == 0 && warp == 0) {        // the sink joins one warp's share, once
+        m[0] = m[1] = 0.f;
+        l[0] = l[1] = t == 0 ? 1.f : 0.f;
+    }
     float o[D / 8][4];
 #pragma unroll
     for (int n = 0; n < D / 8; ++n)
@@ -757,7 +807,7 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
     const float scale_log2 = a.scale * LOG2E;
 
     if (first < t_end && deferred) {
-        if (a.p_shift >= 0) loader.lookup(bt_row, j_begin + first * 32, lo, pos);
+        if (a.p_shift >= 0) look(first);
         issue(first, 0);
     }
     int stage = 0;
@@ -766,7 +816,8 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
         if (more) issue(tile + 4, stage ^ 1);
         if (more) cp_async_wait<1>(); else cp_async_wait<0>();
         __syncwarp();
-        const int j0 = j_begin + tile * 32;
+        int j0, j_lo, j_hi;
+        range(tile, j0, j_lo, j_hi);
         const uint32_t off = (uint32_t)warp * 4 * TILE_BYTES + (uint32_t)stage * 2 * TILE_BYTES;
         if (a.write_kv && tile == last_tile) {
             // this step's key and value: into their row of the tile (the copies left it zero)
@@ -779,7 +830,11 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
             __syncwarp();
         }
         const uint32_t base = smem_u32(smem_raw) + off;
-        warp_block<D, 32>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2, true, m, l, o);
+        if (X && keep_first > 0)
+            warp_block<D, 32>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2, true, m, l, o,
+                              keep_first, j_lo, tile < n_keep ? j_hi : pos);
+        else
+            warp_block<D, 32>(qf, base, base + TILE_BYTES, j0, pos_lo, pos_hi, window, scale_log2, true, m, l, o);
         __syncwarp();
         stage ^= 1;
     }
@@ -808,6 +863,11 @@ __global__ void __launch_bounds__(128) attn_decode_fused_kernel(const DecodeFuse
     __syncthreads();
     // one finished element: rounded as the attention's output, gated, rounded again
     auto finish = [&](int head, int c, float val) {
+        if (X && a.opt.gate_mode == 2) {                     // a gate per element: one rounding
+            a.out[((size_t)tok * H + head) * D + c] =
+                __float2bfloat16_rn(val * elem_gate_of(a.gate, a.ldg, tok, head * D + c));
+            return;
+        }
         float y = round_as<__nv_bfloat16>(val);
         if (a.gate != nullptr) {
             const float gv = __bfloat162float(a.gate[(size_t)tok * a.ldg + head]);
@@ -1098,12 +1158,23 @@ TK_API int tk_attn_decode_fused_max_splits(int H, int Hkv, int D) {
 // split between shared memory and L1 only when it is empty, so a kernel that asks for another
 // split than its neighbours cannot start under them, and the split it leaves behind is the L1 the
 // next kernels' loads find.
-TK_API int tk_attn_decode_fused(const void* qkv, int64_t ldq, void* kv_pool, void* out, const float* wq,
-                                const float* wk, float eps, const float* inv_freq, int R,
-                                const void* gate, int64_t ldg, const int* positions, const int* tok_seq,
-                                const int* block_table, int bt_stride, int n, int H, int Hkv, int D, int P,
-                                int window, float scale, int nsplit, float* scratch, int* tickets,
-                                int write_kv, int carveout, cudaStream_t stream) {
+// general != 0: the kernel's general form: cos and sin times cs_mult and not rounded, pairs
+// (2i, 2i + 1) when interleaved, qkv without value heads when v_is_k (the value is the key as
+// projected), kept first positions, a sink, gate_mode 2 = a gate per output element [n, H * D].
+TK_API int tk_attn_decode_fused_opt(const void* qkv, int64_t ldq, void* kv_pool, void* out, const float* wq,
+                                    const float* wk, float eps, const float* inv_freq, int R,
+                                    const void* gate, int64_t ldg, const int* positions, const int* tok_seq,
+                                    const int* block_table, int bt_stride, int n, int H, int Hkv, int D, int P,
+                                    int window, float scale, int nsplit, float* scratch, int* tickets,
+                                    int write_kv, int carveout, int general, float cs_mult, int interleaved,
+                                    int v_is_k, int keep_first, int sink, int gate_mode, cudaStream_t stream) {
+    TK_CHECK_ARG(general || (!interleaved && !v_is_k && keep_first == 0 && !sink && gate_mode != 2),
+                 "attn_decode_fused: the options belong to the general form");
+    TK_CHECK_ARG(!general || (wq == nullptr && wk == nullptr), "attn_decode_fused: the general form norms no heads");
+    TK_CHECK_ARG(keep_first >= 0 && (keep_first == 0 || window > 0), "attn_decode_fused: kept first positions need a window");
+    TK_CHECK_ARG(gate_mode >= 0 && gate_mode <= 2 && (gate_mode == 0) == (gate == nullptr),
+                 "attn_decode_fused: gate mode %d and the gate do not go together", gate_mode);
+    TK_CHECK_ARG(!v_is_k || write_kv, "attn_decode_fused: values that are the keys are written with them");
     TK_CHECK_ARG(tk_attn_decode_fused_supported(H, Hkv, D, R),
                  "attn_decode_fused: shape H=%d Hkv=%d D=%d rotary %d is not taken (head size 64 or 128, "
                  "group a power of two up to 16, rotary width a multiple of 16)", H, Hkv, D, R);
@@ -1144,12 +1215,24 @@ TK_API int tk_attn_decode_fused(const void* qkv, int64_t ldq, void* kv_pool, voi
     a.tickets = tickets;
     a.p_shift = page_shift(P);
     a.write_kv = write_kv ? 1 : 0;
+    a.cs_mult = cs_mult;
+    a.interleaved = interleaved ? 1 : 0;
+    a.v_is_k = v_is_k ? 1 : 0;
+    a.opt = AttnOptions{keep_first, sink ? 1 : 0, gate_mode};
     dim3 grid(n, Hkv, nsplit);
     // K/V staging (the warps' merge reuses it), the query tile, the new key and value, cos and sin
     const size_t smem = 4 * 2 * 2 * 32 * (size_t)D * 2 + 16 * ((size_t)D + 8) * 2 + 2 * (size_t)D * 2 +
                         (size_t)D * sizeof(float);
     const int prefer = carveout >= 0 && carveout <= 100 ? carveout : (int)cudaSharedmemCarveoutDefault;
-    if (D == 64) {
+    if (general && D == 64) {
+        cudaFuncSetAttribute(attn_decode_fused_kernel<64, true>, cudaFuncAttributePreferredSharedMemoryCarveout, prefer);
+        cudaFuncSetAttribute(attn_decode_fused_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_fused_kernel<64, true>, dim3(grid), dim3(128), smem, stream, a);
+    } else if (general) {
+        cudaFuncSetAttribute(attn_decode_fused_kernel<128, true>, cudaFuncAttributePreferredSharedMemoryCarveout, prefer);
+        cudaFuncSetAttribute(attn_decode_fused_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        tk_launch(attn_decode_fused_kernel<128, true>, dim3(grid), dim3(128), smem, stream, a);
+    } else if (D == 64) {
         cudaFuncSetAttribute(attn_decode_fused_kernel<64>, cudaFuncAttributePreferredSharedMemoryCarveout, prefer);
         cudaFuncSetAttribute(attn_decode_fused_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         tk_launch(attn_decode_fused_kernel<64>, dim3(grid), dim3(128), smem, stream, a);
@@ -1160,6 +1243,17 @@ TK_API int tk_attn_decode_fused(const void* qkv, int64_t ldq, void* kv_pool, voi
     }
     TK_CHECK_LAUNCH("attn_decode_fused");
     return 0;
+}
+
+TK_API int tk_attn_decode_fused(const void* qkv, int64_t ldq, void* kv_pool, void* out, const float* wq,
+                                const float* wk, float eps, const float* inv_freq, int R,
+                                const void* gate, int64_t ldg, const int* positions, const int* tok_seq,
+                                const int* block_table, int bt_stride, int n, int H, int Hkv, int D, int P,
+                                int window, float scale, int nsplit, float* scratch, int* tickets,
+                                int write_kv, int carveout, cudaStream_t stream) {
+    return tk_attn_decode_fused_opt(qkv, ldq, kv_pool, out, wq, wk, eps, inv_freq, R, gate, ldg, positions, tok_seq,
+                                    block_table, bt_stride, n, H, Hkv, D, P, window, scale, nsplit, scratch, tickets,
+                                    write_kv, carveout, 0, 1.0f, 0, 0, 0, 0, gate != nullptr ? 1 : 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -553,7 +553,9 @@ def attention_decode_fused(qkv: torch.Tensor, kv_pool: torch.Tensor, q_norm: tor
                            gate: torch.Tensor | None, positions: torch.Tensor, tok_seq: torch.Tensor,
                            block_table: torch.Tensor, heads: int, kv_heads: int, window: int | None,
                            scale: float, nsplit: int, write_kv: bool = True,
-                           carveout: int = -1) -> torch.Tensor:
+                           carveout: int = -1, general: bool = False, cs_mult: float = 1.0,
+                           interleaved: bool = False, v_is_k: bool = False, keep_first: int = 0,
+                           sink: bool = False, gate_by_element: bool = False) -> torch.Tensor:
     """A decode step's attention in one kernel, for sequences that bring one token each (row i of
     ``qkv`` is sequence i's): from the raw projection rows ``qkv`` [T, >= (H + 2 Hkv) D] (q heads,
     k heads, v heads; rows may be strided) through q/k norm, the rotate-half rotation by
@@ -563,17 +565,26 @@ def attention_decode_fused(qkv: torch.Tensor, kv_pool: torch.Tensor, q_norm: tor
     [T, H, D]. ``write_kv`` False: the layer reads a cache that another layer wrote this step and
     ``qkv`` holds queries only. ``carveout``: the share of an SM's memory, in percent of the most,
     that the launch prefers as shared memory (-1: the driver's choice). ``nsplit`` is cut to what
-    the kernel's merge can hold."""
+    the kernel's merge can hold.
+    ``general``: the kernel's general form, without head norms: cos and sin are multiplied by
+    ``cs_mult`` and not rounded, columns pair (2i, 2i + 1) when ``interleaved``, ``qkv`` holds no
+    value heads when ``v_is_k`` (a key as projected is its value), ``keep_first`` positions stay
+    visible behind the window, ``sink`` adds one to the softmax's denominator, and with
+    ``gate_by_element`` the gate is [T, H * D], applied to the 32-bit output before its one rounding."""
     _cuda(qkv, kv_pool, q_norm, k_norm, inv_freq, gate, positions, tok_seq, block_table)
     T = qkv.shape[0]
     _, two, Hkv, P, D = kv_pool.shape
-    need = (heads + (2 * Hkv if write_kv else 0)) * D
+    need = (heads + ((1 if v_is_k else 2) * Hkv if write_kv else 0)) * D
     if (two != 2 or Hkv != kv_heads or qkv.dtype != torch.bfloat16 or kv_pool.dtype != torch.bfloat16
             or qkv.stride(1) != 1 or qkv.shape[1] < need or not kv_pool.is_contiguous()):
         raise KernelError("attention_decode_fused: qkv [T, >= (H + 2 Hkv) D] with contiguous rows and "
                           "kv_pool [pages, 2, Hkv, P, D], both bfloat16")
-    if gate is not None and (gate.dtype != torch.bfloat16 or gate.shape != (T, heads) or gate.stride(1) != 1):
-        raise KernelError("attention_decode_fused: gate must be a bfloat16 [T, H] view with unit column stride")
+    gate_cols = heads * D if gate_by_element else heads
+    if gate is not None and (gate.dtype != torch.bfloat16 or gate.shape != (T, gate_cols) or gate.stride(1) != 1):
+        raise KernelError(f"attention_decode_fused: gate must be a bfloat16 [T, {gate_cols}] view with unit "
+                          "column stride")
+    if not general and (interleaved or v_is_k or keep_first or sink or gate_by_element or cs_mult != 1.0):
+        raise KernelError("attention_decode_fused: these options belong to the general form")
     R = 2 * inv_freq.numel()
     out = torch.empty(T, heads, D, dtype=torch.bfloat16, device=qkv.device)
     nsplit = max(1, min(int(nsplit), _lib.call("tk_attn_decode_fused_max_splits", heads, Hkv, D)))
@@ -581,13 +592,15 @@ def attention_decode_fused(qkv: torch.Tensor, kv_pool: torch.Tensor, q_norm: tor
     if nsplit > 1:
         scratch = torch.empty(T * heads * nsplit * (D + 2), dtype=torch.float32, device=qkv.device)
         tickets = _decode_tickets(T * Hkv, qkv.device)
-    _lib.call("tk_attn_decode_fused", _ptr(qkv), qkv.stride(0), _ptr(kv_pool), _ptr(out),
+    _lib.call("tk_attn_decode_fused_opt", _ptr(qkv), qkv.stride(0), _ptr(kv_pool), _ptr(out),
               _ptr(_f32vec(q_norm, "q_norm", D)), _ptr(_f32vec(k_norm, "k_norm", D)), float(eps),
               _ptr(_f32vec(inv_freq, "inv_freq", R // 2)), R, _ptr(gate),
               gate.stride(0) if gate is not None else 0, _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
               T, heads, Hkv, D, P, int(window or 0), float(scale), int(nsplit), _ptr(scratch), _ptr(tickets),
-              1 if write_kv else 0, int(carveout), _stream())
+              1 if write_kv else 0, int(carveout), int(bool(general)), float(cs_mult), int(bool(interleaved)),
+              int(bool(v_is_k)), int(keep_first), int(bool(sink)),
+              0 if gate is None else (2 if gate_by_element else 1), _stream())
     return out
 
 

@@ -54,6 +54,8 @@ _SIGNATURES = {
     "tk_attn_decode_mma": [P, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, P, P, L, P],
     "tk_attn_decode_fused_supported": [I, I, I, I],
     "tk_attn_decode_fused_max_splits": [I, I, I],
+    "tk_attn_decode_fused_opt": [P, L, P, P, P, P, F, P, I, P, L, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, I,
+                                 I, F, I, I, I, I, I, P],
     "tk_attn_decode_fused": [P, L, P, P, P, P, F, P, I, P, L, P, P, P, I, I, I, I, I, I, I, F, I, P, P, I, I, P],
     "tk_conv_min_tile": [I],
     "tk_conv_gated": [P, L, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],

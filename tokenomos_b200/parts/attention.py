@@ -83,6 +83,7 @@ class Attention:
             raise ValueError("attention: the fused projection does not match the head counts")
         self.norm_folded = False
         self._fused_freqs = None        # the rotation's frequencies once asked for; False: not fusable
+        self._fused_general = None      # the options of the one-kernel decode form's general variant
         self.head_layout = HeadLayout(heads, own_kv, head_dim, self.q_norm,
                                       self.k_norm if own_kv else None, self.eps,
                                       v_dim=v_dim, v_is_k=self.v_is_k)
@@ -138,12 +139,24 @@ class Attention:
     def _fused_decode(self, ctx: StepContext) -> bool:
         """Whether this step's attention runs as one kernel: every sequence brings one token, the
         position encoding is a plain rotation that says so, and the kernel takes the shape."""
-        if not (self.decode_fused and ctx.host.decode_only and self.gate is None and not self.extended
+        if not (self.decode_fused and ctx.host.decode_only and self.gate is None
                 and ctx.n_tokens <= self.tuning.decode_fused_rows):
             return False
         if self._fused_freqs is None:
+            self._fused_general = None
             offer = getattr(self.rope, "rotate_half_frequencies", None)
-            freqs = offer() if offer is not None else None
+            general = getattr(self.rope, "plain_rotation", None)
+            freqs = None
+            if offer is not None and not self.extended:
+                freqs = offer()
+            elif (general is not None and self.v_dim == self.head_dim and self.q_norm is None
+                  and self.k_norm is None and self.kv_source is None
+                  and self.head_dim <= self.tuning.decode_fused_general_head):
+                # the kernel's general form: any plain rotation, and this part's options
+                freqs, cs_mult, interleaved = general()
+                self._fused_general = dict(general=True, cs_mult=cs_mult, interleaved=interleaved,
+                                           v_is_k=self.v_is_k, keep_first=self.keep_first, sink=self.sink,
+                                           gate_by_element=self.gate_kind == "element")
             self._fused_freqs = freqs if freqs is not None and ops.attention_decode_fused_supported(
                 self.heads, self.kv_heads, self.head_dim, 2 * freqs.numel(), self.qkv.weight.dtype) else False
         return self._fused_freqs is not False
@@ -159,12 +172,13 @@ class Attention:
             longest = min(longest, self.window)
         nsplit = self.fused_splits(ctx.n_tokens, self.kv_heads, longest, self.tuning)
         n = self.qkv_width
-        gate = proj[:, n:n + self.heads] if self.gate_fused else None
+        gate = proj[:, n:n + self.gate_width] if self.gate_fused else None
         return ops.attention_decode_fused(
             proj, pool, layout.q_norm, layout.k_norm if layout.kv_heads else None, layout.eps,
             self._fused_freqs, gate, ctx.positions, ctx.tok_seq, table, self.heads, self.kv_heads,
             self.window, self.scale, nsplit, write_kv=bool(layout.kv_heads),
-            carveout=self.tuning.decode_fused_carveout if ctx.n_tokens <= self.tuning.skinny_rows else -1)
+            carveout=self.tuning.decode_fused_carveout if ctx.n_tokens <= self.tuning.skinny_rows else -1,
+            **(self._fused_general or {}))
 
     def _core(self, qkv: torch.Tensor, ctx: StepContext, call: int,
               gate: torch.Tensor | None = None) -> torch.Tensor:

@@ -39,6 +39,10 @@ class Tuning:
     split attention, merge and gate are one kernel (``ops.attention_decode_fused``); beyond, the
     separate kernels overlap better (measured: -2.7 % of the step at 1 row, -5 % at 8, +1 % at 16,
     +5 % at 64). ``decode_fused_ctas_per_sm``: how many of its CTAs an SM holds (``Attention.fused_splits``).
+    ``decode_fused_general_head``: the largest head size at which the kernel's general form
+    (any plain rotation, sink, kept first positions, gate per element) is taken: at 64 it beats
+    the separate kernels (0.471 against 0.498 ms a step of 8 rows at width 2,048), at 128, where
+    one CTA fills an SM's shared memory, it loses (0.560 against 0.507 ms).
     ``decode_fused_carveout``: the share of shared memory that
     kernel asks for (percent) while the products around it are the weight-streaming kernels (up to
     ``skinny_rows`` rows): an SM changes its split between shared memory and L1 only when empty,
@@ -70,6 +74,7 @@ class Tuning:
     decode_ctas_per_sm: int = 12
     decode_fused_rows: int = 8
     decode_fused_ctas_per_sm: int = 2
+    decode_fused_general_head: int = 64
     decode_fused_carveout: int = 62
     prefill_split_ctas_per_sm: int = 2
     prefill_split_scratch_mb: int = 64

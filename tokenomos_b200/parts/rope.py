@@ -104,6 +104,12 @@ class Rotary:
             out.append(f / factor * ramp + f * (1.0 - ramp))
         return out, 0.1 * math.log(factor) + 1.0
 
+    def plain_rotation(self) -> tuple[torch.Tensor, float, bool]:
+        """(frequencies [dims / 2] float32, the factor on cos and sin, whether columns pair
+        (2i, 2i + 1)): all there is to this encoding, for a mixer that applies it inside a kernel
+        of its own (attention does, in steps where every sequence brings one token)."""
+        return self.freq, self.cs_mult, self.interleaved
+
     def encode_qk(self, qkv: torch.Tensor, ctx: StepContext, heads: HeadLayout,
                   pool: torch.Tensor | None, table: torch.Tensor | None) -> torch.Tensor:
         if heads.q_norm is not None or heads.k_norm is not None:
