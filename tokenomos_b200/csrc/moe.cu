@@ -1,0 +1,305 @@
+// Mixture of experts: routing, the sort of (token, expert) pairs into per-expert row blocks, a
+// grouped / batched matrix product on the CUDA cores, and the weighted combination.
+//
+//   route:   s = softmax(z[0:E]) (32-bit); the `top` largest (ties: the lowest index);
+//            w_k = s_k / (sum of the chosen s + 1e-20) * scale;  gate = sigmoid(z[E]) if the row has one
+//   sort:    pairs (token, k) grouped by expert, every expert's block padded to whole tiles of
+//            `tile` rows, so that a tile of the product belongs to one expert
+//   product: C[m, :] = act(A[row(m), :] . W[g]^T), g the group of m's tile (or the batch index)
+//   combine: out[t] = sum_k w[t, k] * Y[row of (t, k)] + gate[t] * shared[t]
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+constexpr int ROUTE_WARPS = 4;
+constexpr int MAX_TOP = 32;
+constexpr int TM = 64, TN = 64, TKK = 16, GEMM_THREADS = 256;
+}  // namespace
+
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const float* logits, int64_t ld, int tokens, int E, int top, float scale, int has_gate,
+                 int* idx_out, float* w_out, float* gate_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * ROUTE_WARPS + warp;
+    if (t >= tokens) return;
+    float* z = smem + (size_t)warp * E;
+    const float* row = logits + (size_t)t * ld;
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) {
+        const float v = row[e];
+        z[e] = v;
+        mx = fmaxf(mx, v);
+    }
+    mx = warp_max(mx);
+    if (!(mx > -INFINITY)) mx = 0.f;                // a row without a finite value (padding of a recorded step)
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+        const float p = expf(z[e] - mx);
+        z[e] = p;
+        sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    float chosen_sum = 0.f;
+    float my_w = 0.f;                               // lane k keeps the k-th chosen score
+    int my_e = 0;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float v = z[e];
+            if (v > best) { best = v; at = e; }     // ascending e: the lowest index of equal values stays
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (at == 0x7fffffff) { at = k < E ? k : 0; best = 0.f; }    // nothing comparable: stay inside the table
+        if (lane == 0) z[at] = -INFINITY;
+        __syncwarp();
+        const float s = best / sum;
+        chosen_sum += s;
+        if (lane == (k & 31)) { my_w = s; my_e = at; }
+    }
+    if (lane < top) {
+        idx_out[(size_t)t * top + lane] = my_e;
+        w_out[(size_t)t * top + lane] = my_w / (chosen_sum + 1e-20f) * scale;
+    }
+    if (has_gate && lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-row[E]));
+}
+
+TK_API int tk_moe_route(const float* logits, int64_t ld, int tokens, int E, int top, float scale, int has_gate,
+                        int* idx_out, float* w_out, float* gate_out, cudaStream_t stream) {
+    TK_CHECK_ARG(tokens >= 0 && E > 0 && top > 0 && top <= E && top <= MAX_TOP, "moe_route: %d of %d experts (at most %d)",
+                 top, E, MAX_TOP);
+    TK_CHECK_ARG((size_t)E * ROUTE_WARPS * 4 <= 48 * 1024, "moe_route: %d experts do not fit shared memory", E);
+    TK_CHECK_ARG(ld >= E + (has_gate ? 1 : 0), "moe_route: rows of %lld for %d experts", (long long)ld, E);
+    if (tokens == 0) return 0;
+    tk_launch(moe_route_kernel, dim3((tokens + ROUTE_WARPS - 1) / ROUTE_WARPS), dim3(ROUTE_WARPS * 32),
+              (size_t)E * ROUTE_WARPS * sizeof(float), stream, logits, ld, tokens, E, top, scale, has_gate, idx_out,
+              w_out, gate_out);
+    TK_CHECK_LAUNCH("moe_route");
+    return 0;
+}
+
+// One block. row_token[cap_rows]: the token whose input a row of the sorted layout reads (-1:
+// padding); pair_row[pairs]: where pair (token * top + k) sits; tile_expert[cap_rows / tile]: the
+// expert of each tile (-1: unused).
+__global__ void __launch_bounds__(1024)
+moe_sort_kernel(const int* idx, int pairs, int top, int E, int tile, int cap_rows, int* row_token, int* pair_row,
+                int* tile_expert) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ int ism[];
+    int* count = ism;
+    int* start = ism + E;
+    int* cursor = ism + 2 * E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0, cursor[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&count[idx[p]], 1);
+    for (int r = threadIdx.x; r < cap_rows; r += blockDim.x) row_token[r] = -1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            start[e] = at;
+            const int tiles = (count[e] + tile - 1) / tile;
+            for (int k = 0; k < tiles; ++k) tile_expert[at / tile + k] = e;
+            at += tiles * tile;
+        }
+        for (int k = at / tile; k < cap_rows / tile; ++k) tile_expert[k] = -1;
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = idx[p];
+        const int r = start[e] + atomicAdd(&cursor[e], 1);
+        row_token[r] = p / top;
+        pair_row[p] = r;
+    }
+}
+
+TK_API int tk_moe_sort(const int* idx, int pairs, int top, int E, int tile, int cap_rows, int* row_token,
+                       int* pair_row, int* tile_expert, cudaStream_t stream) {
+    TK_CHECK_ARG(pairs >= 0 && top > 0 && E > 0 && tile > 0, "moe_sort: bad sizes");
+    TK_CHECK_ARG(cap_rows % tile == 0 && cap_rows >= pairs + (E < pairs ? E : pairs) * (tile - 1),
+                 "moe_sort: %d rows cannot hold %d pairs of %d experts in tiles of %d", cap_rows, pairs, E, tile);
+    TK_CHECK_ARG((size_t)E * 12 <= 48 * 1024, "moe_sort: %d experts do not fit shared memory", E);
+    if (pairs == 0) return 0;
+    tk_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), stream, idx, pairs, top, E, tile,
+              cap_rows, row_token, pair_row, tile_expert);
+    TK_CHECK_LAUNCH("moe_sort");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// C[m, n] = act(sum_k A[row(m), k] * W[g][n, k]) on the CUDA cores, 32-bit FMA accumulation.
+// Grouped (tile_group given): m runs over the sorted layout, the group of a 64-row tile is
+// tile_group[tile] (-1: nothing to do), row(m) = row_index[m] if given (-1: a row of zeros).
+// Batched (no tile_group): blockIdx.z is the group; A, W and C advance by their group strides.
+// act 1: relu(v)^2.
+// ---------------------------------------------------------------------------------------------
+template <typename TA, typename TO>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_grouped_simt_kernel(const TA* A, int64_t lda, int64_t a_gs, const int* row_index,
+                         const TA* __restrict__ W, int64_t ldw, int64_t w_gs, const int* tile_group, TO* C,
+                         int64_t ldc, int64_t c_gs, int M, int N, int K, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float As[TKK][TM + 4];
+    __shared__ float Ws[TKK][TN + 4];
+    __shared__ int rows_s[TM];
+    const int tid = threadIdx.x;
+    const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+    if (tile_group != nullptr) {
+        const int g = tile_group[blockIdx.y];
+        if (g < 0) return;
+        W += (size_t)g * w_gs;
+    } else {
+        A += (size_t)blockIdx.z * a_gs;
+        W += (size_t)blockIdx.z * w_gs;
+        C += (size_t)blockIdx.z * c_gs;
+    }
+    if (tid < TM) {
+        const int m = m0 + tid;
+        rows_s[tid] = m < M ? (row_index != nullptr ? row_index[m] : m) : -1;
+    }
+    __syncthreads();
+    const int tx = tid & 15, ty = tid >> 4;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;
+    const int arow = rows_s[lr];
+    for (int k0 = 0; k0 < K; k0 += TKK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = k0 + lk + e;
+            const int n = n0 + lr;
+            As[lk + e][lr] = (arow >= 0 && k < K) ? to_f<TA>(A[(size_t)arow * lda + k]) : 0.f;
+            Ws[lk + e][lr] = (n < N && k < K) ? to_f<TA>(W[(size_t)n * ldw + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < TKK; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[k][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[k][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (act == 1) { v = fmaxf(v, 0.f); v *= v; }
+            C[(size_t)m * ldc + n] = from_f<TO>(v);
+        }
+    }
+}
+
+TK_API int tk_gemm_grouped_tile() { return TM; }
+
+TK_API int tk_gemm_grouped_simt(const void* A, int64_t lda, int64_t a_gs, const int* row_index, const void* W,
+                                int64_t ldw, int64_t w_gs, const int* tile_group, void* C, int64_t ldc,
+                                int64_t c_gs, int M, int N, int K, int groups, int act, int dtype,
+                                cudaStream_t stream) {
+    TK_CHECK_ARG(M >= 0 && N > 0 && K > 0 && groups >= 1, "gemm_grouped: bad sizes M=%d N=%d K=%d", M, N, K);
+    TK_CHECK_ARG(ldw >= K && ldc >= N, "gemm_grouped: leading dimensions too small");
+    TK_CHECK_ARG(act == 0 || act == 1, "gemm_grouped: activation %d", act);
+    if (M == 0) return 0;
+    dim3 grid((N + TN - 1) / TN, (M + TM - 1) / TM, tile_group != nullptr ? 1 : groups);
+    if (dtype == TK_F32)
+        tk_launch(gemm_grouped_simt_kernel<float, float>, grid, dim3(GEMM_THREADS), 0, stream, (const float*)A, lda,
+                  a_gs, row_index, (const float*)W, ldw, w_gs, tile_group, (float*)C, ldc, c_gs, M, N, K, act);
+    else if (dtype == TK_BF16)
+        tk_launch(gemm_grouped_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(GEMM_THREADS), 0, stream,
+                  (const __nv_bfloat16*)A, lda, a_gs, row_index, (const __nv_bfloat16*)W, ldw, w_gs, tile_group,
+                  (__nv_bfloat16*)C, ldc, c_gs, M, N, K, act);
+    else
+        TK_CHECK_ARG(false, "gemm_grouped: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("gemm_grouped_simt");
+    return 0;
+}
+
+// out[t] = sum_k w[t, k] * Y[pair_row[t * top + k]] + gate[t] * shared[t]   (32-bit sum, one rounding)
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const T* Y, const int* pair_row, const float* w, const T* shared, const float* gate, T* out,
+                   int top, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ int rows[MAX_TOP];
+    __shared__ float ws[MAX_TOP];
+    const size_t t = blockIdx.x;
+    if (threadIdx.x < top) {
+        rows[threadIdx.x] = pair_row[t * top + threadIdx.x];
+        ws[threadIdx.x] = w[t * top + threadIdx.x];
+    }
+    __syncthreads();
+    const float g = shared != nullptr ? (gate != nullptr ? gate[t] : 1.f) : 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = 0.f;
+        for (int k = 0; k < top; ++k) v = fmaf(ws[k], to_f<T>(Y[(size_t)rows[k] * width + i]), v);
+        if (shared != nullptr) v = fmaf(g, to_f<T>(shared[t * width + i]), v);
+        out[t * width + i] = from_f<T>(v);
+    }
+}
+
+TK_API int tk_moe_combine(const void* Y, const int* pair_row, const float* w, const void* shared,
+                          const float* gate, void* out, int tokens, int top, int width, int dtype,
+                          cudaStream_t stream) {
+    TK_CHECK_ARG(tokens >= 0 && top > 0 && top <= MAX_TOP && width > 0, "moe_combine: bad sizes");
+    if (tokens == 0) return 0;
+    if (dtype == TK_F32)
+        tk_launch(moe_combine_kernel<float>, dim3(tokens), dim3(256), 0, stream, (const float*)Y, pair_row, w,
+                  (const float*)shared, gate, (float*)out, top, width);
+    else if (dtype == TK_BF16)
+        tk_launch(moe_combine_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), 0, stream, (const __nv_bfloat16*)Y,
+                  pair_row, w, (const __nv_bfloat16*)shared, gate, (__nv_bfloat16*)out, top, width);
+    else
+        TK_CHECK_ARG(false, "moe_combine: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("moe_combine");
+    return 0;
+}
+
+// x = relu(x)^2 in place
+template <typename T>
+__global__ void relu2_kernel(T* x, size_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f<T>(x[i]), 0.f);
+        x[i] = from_f<T>(v * v);
+    }
+}
+
+TK_API int tk_relu2(void* x, int64_t n, int dtype, cudaStream_t stream) {
+    TK_CHECK_ARG(n >= 0, "relu2: bad size");
+    if (n == 0) return 0;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    if (dtype == TK_F32) tk_launch(relu2_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (size_t)n);
+    else if (dtype == TK_BF16)
+        tk_launch(relu2_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, (size_t)n);
+    else TK_CHECK_ARG(false, "relu2: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("relu2");
+    return 0;
+}

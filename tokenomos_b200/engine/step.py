@@ -189,7 +189,7 @@ class _DecodeGraph:
         from tokenomos_b200 import ops
         from tokenomos_b200.sampling import sampler
 
-        h = model.embed_fed(self.ids_host, self.use_prev, self.last_token, self.ctx.seq_slot)
+        h = model.embed_fed(self.ids_host, self.use_prev, self.last_token, self.ctx.seq_slot, self.ctx)
         out = model.forward(h, self.ctx)
         logits = model.logits(out, None)          # every row is wanted, in order
         sampler.sample_packed(logits, self.sampling, self.tokens,
@@ -318,7 +318,7 @@ class _StepGraph:
         from tokenomos_b200.sampling import sampler
 
         v = self.view
-        h = model.embed_fed(v("ids_host"), v("use_prev"), self.last_token, v("tok_slot"))
+        h = model.embed_fed(v("ids_host"), v("use_prev"), self.last_token, v("tok_slot"), self.ctx)
         out = model.forward(h, self.ctx)
         logits = model.logits(out, v("want"))
         sampler.sample_packed(logits, v("sampling"), self.sampled,
@@ -557,7 +557,7 @@ class StepFunction:
         of their ``want`` lists (None when nothing is wanted). ``commit`` False leaves advancing
         the requests' lengths to the caller (the scheduler does it when it takes the tokens)."""
         ctx, ids, want = self.layout(entries)
-        out = self.model.forward(self.model.embed(ids), ctx)
+        out = self.model.forward(self.model.embed(ids, ctx), ctx)
         if not ctx.host.decode_only:
             self._tiles_known = True
         logits = self.model.logits(out, want) if want.numel() else None

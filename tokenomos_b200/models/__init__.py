@@ -15,6 +15,7 @@ from pathlib import Path
 import torch
 
 from tokenomos_b200.models.darizen import Darizen
+from tokenomos_b200.models.laposun import Laposun
 from tokenomos_b200.models.lfm3 import Lfm3
 from tokenomos_b200.parts import build_model
 from tokenomos_b200.parts.registry import Runtime, Tuning
@@ -93,3 +94,4 @@ def from_tensors(conf: Configured, tensors: dict, device: torch.device | str = "
 
 register(Lfm3())
 register(Darizen())
+register(Laposun())

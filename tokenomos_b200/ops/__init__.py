@@ -792,3 +792,255 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
               _ptr(top_k), _ptr(min_p), _ptr(seed), _ptr(step), _ptr(out), _ptr(idx), _ptr(target),
               _stream())
     return out
+
+
+# ---- several copies of the residual stream, hashed bigram embedding, input convolution --------
+
+HYPER_MAX_STREAMS = 8
+CANON_MAX_TAPS = 8
+
+
+def embed_bigram_norm(table: torch.Tensor, bigram: torch.Tensor | None, norm_w: torch.Tensor | None, eps: float,
+                      ids: torch.Tensor, select: tuple | None, tok_seq: torch.Tensor, cu_seqlens: torch.Tensor,
+                      seq_ctx: torch.Tensor, seq_slot: torch.Tensor, prev_state: torch.Tensor | None,
+                      copies: int, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0) -> torch.Tensor:
+    """``rmsnorm(table[id] + bigram[(prev * mul_prev + id * mul_cur) % buckets]) * norm_w`` in 32-bit,
+    written ``copies`` times side by side: float32 [T, copies * width]. A sequence's first token
+    takes bigram row ``buckets``; the previous token of a portion's first token comes from
+    ``prev_state`` (int32 [slots, 1]), which then takes the portion's last id. ``select``:
+    ``(use_prev, last_token, tok_slot)``, token r reads ``last_token[tok_slot[r]]`` where
+    ``use_prev[r]`` is set instead of ``ids[r]``."""
+    _cuda(table, bigram, norm_w, ids, tok_seq, cu_seqlens, seq_ctx, seq_slot, prev_state)
+    T, width = ids.numel(), table.shape[1]
+    if not table.is_contiguous() or (bigram is not None and (not bigram.is_contiguous() or bigram.dtype != table.dtype
+                                                             or tuple(bigram.shape) != (buckets + 1, width))):
+        raise KernelError("embed_bigram_norm: tables must be contiguous, of one type, the bigram [buckets + 1, width]")
+    if bigram is not None and (prev_state is None or prev_state.dtype != torch.int32):
+        raise KernelError("embed_bigram_norm: the bigram needs an int32 state")
+    use_prev, last_token, tok_slot = select if select is not None else (None, None, None)
+    out = torch.empty(T, copies * width, dtype=torch.float32, device=table.device)
+    _lib.call("tk_embed_bigram_norm", _ptr(table), _ptr(bigram), _ptr(_f32vec(norm_w, "norm weight", width)),
+              float(eps), _ptr(_i32(ids, "ids")), _ptr(use_prev), _ptr(last_token), _ptr(tok_slot),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(cu_seqlens, "cu_seqlens")), _ptr(_i32(seq_ctx, "seq_ctx")),
+              _ptr(_i32(seq_slot, "seq_slot")), _ptr(prev_state), _ptr(out), T, int(copies), width, table.shape[0],
+              int(buckets), int(mul_prev), int(mul_cur), _dtype_code(table), _stream())
+    return out
+
+
+def hc_mix_norm(streams: torch.Tensor, y: torch.Tensor | None, mix: torch.Tensor | None, out_w: torch.Tensor | None,
+                in_w: torch.Tensor | None, norm_w: torch.Tensor | None, eps: float, n_streams: int,
+                out_dtype: torch.dtype, keep32: bool) -> torch.Tensor | None:
+    """Streams ``[T, S * width]`` float32, in place: ``x'_t = sum_s mix[s, t] x_s + out_w[t] * y``
+    (when ``y`` [T, width] is given; ``mix`` None: identity, ``out_w`` None: ones), then
+    ``h = rmsnorm(sum_s in_w[s] x'_s) * norm_w`` (``in_w`` None: ones): float32 when ``keep32``, else
+    ``out_dtype``. ``norm_w`` None: only the write, returns None."""
+    _cuda(streams, y, mix, out_w, in_w, norm_w)
+    S = int(n_streams)
+    T, width = streams.shape[0], streams.shape[1] // S
+    if streams.dtype != torch.float32 or not streams.is_contiguous() or streams.shape[1] != S * width:
+        raise KernelError("hc_mix_norm: the streams are a contiguous float32 [T, S * width] tensor")
+    if y is not None and (tuple(y.shape) != (T, width) or y.stride(1) != 1 or y.dtype != out_dtype):
+        raise KernelError(f"hc_mix_norm: y {tuple(y.shape)} {y.dtype} for [{T}, {width}] {out_dtype}")
+    h = None
+    if norm_w is not None:
+        h = torch.empty(T, width, dtype=torch.float32 if keep32 else out_dtype, device=streams.device)
+    code = F32 if out_dtype == torch.float32 else BF16
+    _lib.call("tk_hc_mix_norm", _ptr(streams), _ptr(y), y.stride(0) if y is not None else 0,
+              _ptr(_f32vec(mix, "mix", S * S)), _ptr(_f32vec(out_w, "out", S)), _ptr(_f32vec(in_w, "in", S)),
+              _ptr(_f32vec(norm_w, "norm weight", width)), float(eps), _ptr(h if keep32 else None),
+              _ptr(None if keep32 else h), T, S, width, code, _stream())
+    return h
+
+
+def canon_conv(h: torch.Tensor, taps: torch.Tensor, state: torch.Tensor | None, cu_seqlens: torch.Tensor,
+               seq_ctx: torch.Tensor, seq_slot: torch.Tensor, tiles: tuple, out_dtype: torch.dtype) -> torch.Tensor:
+    """``o_t = h_t + sum_j taps[:, j] h_(t - K + 1 + j)`` within each sequence (zeros before its start),
+    ``h`` float32 [T, width], ``taps`` float32 [width, K]; the last K - 1 rows of ``h`` of every
+    sequence are kept in ``state`` (float32 [slots, K - 1, width]). ``tiles``: ``ctx.tiles(size)`` with
+    size >= K - 1."""
+    _cuda(h, taps, state, cu_seqlens, seq_ctx, seq_slot, *tiles)
+    T, width = h.shape
+    K = taps.shape[1]
+    if h.dtype != torch.float32 or not h.is_contiguous() or taps.dtype != torch.float32 or not taps.is_contiguous():
+        raise KernelError("canon_conv: h and taps are contiguous float32 tensors")
+    if K > 1 and (state is None or state.dtype != torch.float32 or tuple(state.shape[1:]) != (K - 1, width)
+                  or not state.is_contiguous()):
+        raise KernelError(f"canon_conv: the state is float32 [slots, {K - 1}, {width}]")
+    seq, tok0, off, n = tiles
+    out = torch.empty(T, width, dtype=out_dtype, device=h.device)
+    _lib.call("tk_canon_conv", _ptr(h), _ptr(taps), _ptr(state), _ptr(_i32(cu_seqlens, "cu_seqlens")),
+              _ptr(_i32(seq_ctx, "seq_ctx")), _ptr(_i32(seq_slot, "seq_slot")), _ptr(_i32(seq, "tile_seq")),
+              _ptr(_i32(tok0, "tile_tok0")), _ptr(_i32(off, "tile_off")), _ptr(_i32(n, "tile_n")), seq.numel(),
+              _ptr(out), K, width, F32 if out_dtype == torch.float32 else BF16, _stream())
+    return out
+
+
+# ---- attention over a cache of latents ----------------------------------------------------------
+
+def latent_prepare(proj: torch.Tensor, wq: torch.Tensor, wkv: torch.Tensor, eps: float, freq: torch.Tensor,
+                   positions: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor, cache: torch.Tensor,
+                   q_rank: int, rank: int, rot_dim: int) -> torch.Tensor:
+    """From the down-projection's rows ``[q latent | kv latent | rotated key part | ...]``: the normed
+    query latent [T, q_rank] (returned), and into ``cache`` [pages, P, rank + rot_dim], at each token's
+    position, the normed kv latent and the key part rotated by ``position * freq`` (pairs (2i, 2i+1),
+    ``2 len(freq)`` columns)."""
+    _cuda(proj, wq, wkv, freq, positions, tok_seq, block_table, cache)
+    T = proj.shape[0]
+    if proj.stride(1) != 1 or proj.shape[1] < q_rank + rank + rot_dim:
+        raise KernelError("latent_prepare: projection rows are too short")
+    if (cache.dim() != 3 or cache.shape[2] != rank + rot_dim or cache.dtype != proj.dtype
+            or not cache.is_contiguous()):
+        raise KernelError(f"latent_prepare: the cache is [pages, page, {rank + rot_dim}] {proj.dtype}")
+    cq = torch.empty(T, q_rank, dtype=proj.dtype, device=proj.device)
+    _lib.call("tk_latent_prepare", _ptr(proj), proj.stride(0), _ptr(_f32vec(wq, "q latent norm", q_rank)),
+              _ptr(_f32vec(wkv, "kv latent norm", rank)), float(eps), _ptr(freq), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
+              _ptr(cq), _ptr(cache), T, q_rank, rank, rot_dim, 2 * freq.numel(), cache.shape[1],
+              _dtype_code(proj), _stream())
+    return cq
+
+
+def latent_rotate_q(q: torch.Tensor, freq: torch.Tensor, positions: torch.Tensor, heads: int, dim: int,
+                    rot_dim: int) -> torch.Tensor:
+    """In place on ``q`` [T, heads * (dim + rot_dim)]: the last ``rot_dim`` columns of every head rotated."""
+    _cuda(q, freq, positions)
+    if not q.is_contiguous() or q.shape[1] != heads * (dim + rot_dim):
+        raise KernelError("latent_rotate_q: q must be contiguous [T, heads * (dim + rot_dim)]")
+    _lib.call("tk_latent_rotate_q", _ptr(q), _ptr(freq), _ptr(_i32(positions, "positions")), q.shape[0], heads, dim,
+              rot_dim, 2 * freq.numel(), _dtype_code(q), _stream())
+    return q
+
+
+def attention_latent_rows() -> int:
+    return _lib.call("tk_attn_latent_rows")
+
+
+ATTENTION_LATENT_MAX_RANK = 512
+
+
+def attention_latent(q_lat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
+                     tok_seq: torch.Tensor, block_table: torch.Tensor, tile_tok0: torch.Tensor,
+                     tile_ntok: torch.Tensor, tokens_per_tile: int, heads: int, dim: int, rot_dim: int,
+                     window: int | None, scale: float) -> torch.Tensor:
+    """Windowed causal attention over the latent cache [pages, P, R + rot_dim]: scores
+    ``(q_lat[h, t] . c_j + q[t, h, dim:] . k_rot_j) * scale``, output ``sum_j p_j c_j`` as [heads, T, R]."""
+    _cuda(q_lat, q, cache, positions, tok_seq, block_table, tile_tok0, tile_ntok)
+    H, T, R = q_lat.shape
+    if (H != heads or not q_lat.is_contiguous() or not q.is_contiguous() or q.shape[0] != T
+            or q.shape[1] != heads * (dim + rot_dim) or cache.shape[2] != R + rot_dim or cache.dtype != q.dtype
+            or q_lat.dtype != q.dtype):
+        raise KernelError("attention_latent: q / cache layouts do not match")
+    out = torch.empty(H, T, R, dtype=q.dtype, device=q.device)
+    _lib.call("tk_attn_latent", _ptr(q_lat), _ptr(q), _ptr(cache), _ptr(out), _ptr(_i32(positions, "positions")),
+              _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
+              _ptr(_i32(tile_tok0, "tile_tok0")), _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(),
+              int(tokens_per_tile), T, H, dim, R, rot_dim, cache.shape[1], int(window or 0), float(scale),
+              _dtype_code(q), _stream())
+    return out
+
+
+def head_gate_transpose(x: torch.Tensor, gate: torch.Tensor | None) -> torch.Tensor:
+    """``out[t, h, :] = x[h, t, :] * sigmoid(gate[t, h])``: [H, T, D] -> [T, H, D]; ``gate`` may be a
+    column block of wider rows."""
+    _cuda(x, gate)
+    H, T, D = x.shape
+    if not x.is_contiguous() or (gate is not None and (gate.stride(1) != 1 or gate.dtype != x.dtype
+                                                       or tuple(gate.shape) != (T, H))):
+        raise KernelError("head_gate_transpose: x contiguous [H, T, D], gate [T, H] of its type")
+    out = torch.empty(T, H, D, dtype=x.dtype, device=x.device)
+    _lib.call("tk_head_gate_transpose", _ptr(x), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
+              T, H, D, _dtype_code(x), _stream())
+    return out
+
+
+# ---- mixture of experts --------------------------------------------------------------------------
+
+def moe_route(logits: torch.Tensor, experts: int, top: int, scale: float, has_gate: bool):
+    """From float32 router rows ``[T, >= experts (+ 1)]``: the ``top`` experts of the largest
+    softmax scores (int32 [T, top]), their scores over their sum times ``scale`` (float32 [T, top]),
+    and ``sigmoid`` of column ``experts`` (float32 [T]) when ``has_gate``."""
+    _cuda(logits)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("moe_route: router rows are float32 with contiguous columns")
+    T = logits.shape[0]
+    idx = torch.empty(T, top, dtype=torch.int32, device=logits.device)
+    w = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    gate = torch.empty(T, dtype=torch.float32, device=logits.device) if has_gate else None
+    _lib.call("tk_moe_route", _ptr(logits), logits.stride(0), T, int(experts), int(top), float(scale),
+              int(bool(has_gate)), _ptr(idx), _ptr(w), _ptr(gate), _stream())
+    return idx, w, gate
+
+
+def gemm_grouped_tile() -> int:
+    return _lib.call("tk_gemm_grouped_tile")
+
+
+def moe_sort(idx: torch.Tensor, experts: int, tile: int):
+    """(token, k) pairs grouped by expert, each expert's rows padded to whole tiles:
+    ``row_token`` [rows] (-1: padding), ``pair_row`` [T * top], ``tile_expert`` [rows / tile] (-1: unused).
+    ``rows`` is the bound ``T * top + min(experts, T * top) * (tile - 1)`` rounded up to whole tiles."""
+    _cuda(idx)
+    T, top = idx.shape
+    pairs = T * top
+    cap = -(-(pairs + min(experts, pairs) * (tile - 1)) // tile) * tile
+    row_token = torch.empty(cap, dtype=torch.int32, device=idx.device)
+    pair_row = torch.empty(pairs, dtype=torch.int32, device=idx.device)
+    tile_expert = torch.empty(cap // tile, dtype=torch.int32, device=idx.device)
+    _lib.call("tk_moe_sort", _ptr(_i32(idx, "idx")), pairs, top, int(experts), int(tile), cap, _ptr(row_token),
+              _ptr(pair_row), _ptr(tile_expert), _stream())
+    return row_token, pair_row, tile_expert
+
+
+def gemm_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row_index: torch.Tensor | None,
+                 rows: int, act: bool = False) -> torch.Tensor:
+    """``out[m] = act(a[row_index[m]] @ w[g].T)`` with ``g = tile_group[m // tile]``; ``w`` [G, N, K];
+    a row index of -1 reads zeros, a tile group of -1 is skipped (its rows are not written)."""
+    _cuda(a, w, tile_group, row_index)
+    G, N, K = w.shape
+    if a.dtype != w.dtype or a.stride(1) != 1 or not w.is_contiguous() or a.shape[1] != K:
+        raise KernelError(f"gemm_grouped: a {tuple(a.shape)} {a.dtype} against w {tuple(w.shape)} {w.dtype}")
+    out = torch.empty(rows, N, dtype=a.dtype, device=a.device)
+    _lib.call("tk_gemm_grouped_simt", _ptr(a), a.stride(0), 0, _ptr(row_index), _ptr(w), K, N * K,
+              _ptr(_i32(tile_group, "tile_group")), _ptr(out), N, 0, rows, N, K, G, int(bool(act)), _dtype_code(a),
+              _stream())
+    return out
+
+
+def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[g] = a[g] @ w[g].T`` on the CUDA cores (32-bit FMA): ``a`` [G, M, K] (any strides with
+    contiguous columns), ``w`` [G, N, K] likewise, ``out`` [G, M, N]."""
+    _cuda(a, w, out)
+    G, M, K = a.shape
+    N = w.shape[1]
+    if a.dtype != w.dtype or a.stride(2) != 1 or w.stride(2) != 1 or w.shape[0] != G or w.shape[2] != K:
+        raise KernelError(f"gemm_batched: a {tuple(a.shape)} {a.dtype} against w {tuple(w.shape)} {w.dtype}")
+    if out is None:
+        out = torch.empty(G, M, N, dtype=a.dtype, device=a.device)
+    if out.stride(2) != 1:
+        raise KernelError("gemm_batched: out needs contiguous columns")
+    _lib.call("tk_gemm_grouped_simt", _ptr(a), a.stride(1), a.stride(0), None, _ptr(w), w.stride(1), w.stride(0),
+              None, _ptr(out), out.stride(1), out.stride(0), M, N, K, G, 0, _dtype_code(a), _stream())
+    return out
+
+
+def moe_combine(y: torch.Tensor, pair_row: torch.Tensor, w: torch.Tensor, shared: torch.Tensor | None,
+                gate: torch.Tensor | None) -> torch.Tensor:
+    """``out[t] = sum_k w[t, k] * y[pair_row[t * top + k]] + gate[t] * shared[t]`` (32-bit sum)."""
+    _cuda(y, pair_row, w, shared, gate)
+    T, top = w.shape
+    width = y.shape[1]
+    if not y.is_contiguous() or (shared is not None and (not shared.is_contiguous() or shared.dtype != y.dtype)):
+        raise KernelError("moe_combine: contiguous inputs of one type")
+    out = torch.empty(T, width, dtype=y.dtype, device=y.device)
+    _lib.call("tk_moe_combine", _ptr(y), _ptr(_i32(pair_row, "pair_row")), _ptr(w), _ptr(shared), _ptr(gate),
+              _ptr(out), T, top, width, _dtype_code(y), _stream())
+    return out
+
+
+def relu2(x: torch.Tensor) -> torch.Tensor:
+    """In place ``x = relu(x) ** 2``."""
+    _cuda(x)
+    if not x.is_contiguous():
+        raise KernelError("relu2: x must be contiguous")
+    _lib.call("tk_relu2", _ptr(x), x.numel(), _dtype_code(x), _stream())
+    return x

@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 
 from tokenomos_b200 import ops
-from tokenomos_b200.parts.contract import SharedState, StateKey, StateSpec, StepContext
+from tokenomos_b200.parts.contract import EMBED_CALL, SharedState, StateKey, StateSpec, StepContext
 from tokenomos_b200.parts.linear import Linear
 from tokenomos_b200.parts.registry import DEFAULT_TUNING, Tuning, register
 from tokenomos_b200.parts.spec import LayerCall
@@ -92,8 +92,9 @@ class Stack:
     def __init__(self, embedding: torch.Tensor, blocks: list, order: list[LayerCall], final_norm,
                  head: Linear | None, tuning: Tuning = DEFAULT_TUNING, embed_scale: float | None = None,
                  logit_softcap: float | None = None, suppress: tuple[int, ...] = (),
-                 extras: dict[str, torch.Tensor] | None = None):
+                 extras: dict[str, torch.Tensor] | None = None, embedder=None):
         self.embedding = embedding
+        self.embedder = embedder
         self.extras = {name: t.float().contiguous() for name, t in (extras or {}).items()}
         self.embed_scale = None if embed_scale is None else float(embed_scale)
         self.logit_softcap = None if logit_softcap is None else float(logit_softcap)
@@ -131,7 +132,8 @@ class Stack:
     def capture_safe(self) -> bool:
         """Whether a step of this model may be recorded as a CUDA graph: every block (and so
         every part in it) and the final norm say so."""
-        return all(getattr(part, "capture_safe", False) for part in (*self.blocks, self.final_norm))
+        parts = (*self.blocks, self.final_norm) + ((self.embedder,) if self.embedder is not None else ())
+        return all(getattr(part, "capture_safe", False) for part in parts)
 
     def not_capture_safe(self) -> list[str]:
         """The kinds of the parts that keep this model from being recorded."""
@@ -147,21 +149,31 @@ class Stack:
         """Per entry of the layer list, the memory its mixer asks for. An entry that reads
         another's state contributes ``SharedState`` specs pointing at it."""
         out: dict[StateKey, StateSpec] = {}
+        if self.embedder is not None:
+            for name, spec in self.embedder.state_specs().items():
+                out[(EMBED_CALL, name)] = spec
         for i, call in enumerate(self.order):
-            for name, spec in self.blocks[call.block].mixer.state_specs().items():
+            block = self.blocks[call.block]
+            # an arrangement that keeps state of its own (beside its mixer's) lists all of it
+            owner = block if hasattr(block, "state_specs") else block.mixer
+            for name, spec in owner.state_specs().items():
                 if call.state_from is not None:
                     spec = SharedState(call.state_from, name)
                 out[(i, name)] = spec
         return out
 
-    def embed(self, ids: torch.Tensor) -> torch.Tensor:
+    def embed(self, ids: torch.Tensor, ctx: StepContext | None = None) -> torch.Tensor:
+        if self.embedder is not None:
+            return self.embedder.forward(ids, ctx)
         h = ops.gather_rows(self.embedding, ids)
         return h if self.embed_scale is None else ops.scale_rows(h, self.embed_scale)
 
     def embed_fed(self, ids_host: torch.Tensor, use_prev: torch.Tensor, last_token: torch.Tensor,
-                  slot: torch.Tensor) -> torch.Tensor:
+                  slot: torch.Tensor, ctx: StepContext | None = None) -> torch.Tensor:
         """Embedding rows of a decode step whose ids may still be on the device: row r takes
         ``last_token[slot[r]]`` where ``use_prev[r]`` is set, else ``ids_host[r]``."""
+        if self.embedder is not None:
+            return self.embedder.forward(ids_host, ctx, (use_prev, last_token, slot))
         h = ops.gather_rows_select(self.embedding, ids_host, use_prev, last_token, slot)
         return h if self.embed_scale is None else ops.scale_rows(h, self.embed_scale)
 

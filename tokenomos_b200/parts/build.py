@@ -43,6 +43,7 @@ def build_model(spec: ModelSpec, tensors: dict, rt: Runtime) -> Stack:
     final_norm = _part("norm", spec.final_norm, tensors, rt)
     head = Linear(tensors[spec.head.name], tuning=rt.tuning) if spec.head is not None else None
     extras = {name: tensors[decl.name] for name, decl in spec.extras if decl.name in tensors}
+    embedder = _part("embedding", spec.embedder, tensors, rt) if spec.embedder is not None else None
     return Stack(tensors[spec.embedding.name], blocks, list(spec.order), final_norm, head,
                  tuning=rt.tuning, embed_scale=spec.embed_scale, logit_softcap=spec.logit_softcap,
-                 suppress=spec.suppress, extras=extras)
+                 suppress=spec.suppress, extras=extras, embedder=embedder)

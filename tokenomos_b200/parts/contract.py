@@ -83,6 +83,24 @@ class WindowKV:
 
 
 @dataclass(frozen=True)
+class LatentKV:
+    """One row ``[row]`` per position instead of keys and values per head: ``[pages, page, row]``
+    (a compressed key/value latent and whatever rides with it). ``window`` None: every position
+    is kept; else pages behind the window are given back, like ``WindowKV``'s."""
+
+    row: int
+    window: int | None = None
+    storage = "paged"
+
+    @property
+    def group(self) -> tuple:
+        return ("full",) if self.window is None else ("window", self.window)
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        return (page_size, self.row)
+
+
+@dataclass(frozen=True)
 class SlotState:
     """Fixed-size state per request: a row of ``[slots, *shape]``; ``dtype`` None = work dtype."""
 
@@ -101,7 +119,10 @@ class SharedState:
 
 
 # the specs the framework's own parts use; any object with the attributes above is one too
-StateSpec = PagedKV | WindowKV | SlotState | SharedState
+StateSpec = PagedKV | WindowKV | LatentKV | SlotState | SharedState
+# the "call" under which the state of a model's embedding part is keyed (it is no entry of the
+# layer list)
+EMBED_CALL = -1
 # (index of the call in the model's layer list, name of the state within the part)
 StateKey = tuple[int, str]
 

@@ -1,0 +1,104 @@
+"""Latent attention: keys and values of all heads come from one small latent per position.
+
+    c_q = norm(W_dq h) ;  q = W_uq c_q                    per head [dim unrotated | rot_dim rotated]
+    (c, k_rot) = W_dkv h ;  c = norm(c)                   the cache keeps [c | rotate(k_rot)] per position
+    k_h = W_uk[h] c ;  v_h = W_uv[h] c
+    score = (q_nope . k_h + rotate(q_rot) . rotate(k_rot)) * scale ;  softmax over the window
+    out = W_o concat_h(sigmoid(W_g h)_h * sum_j p_j v_h,j)
+
+The up-projections never run over the cache: ``q_nope . (W_uk[h] c) = (W_uk[h]^T q_nope) . c``, so
+the queries are taken into the latent's space (one batched product over the heads), attention
+runs with one shared key/value row per position (key: the whole row, value: its latent part),
+and ``W_uv[h]`` is applied to the attended latent (a second batched product). The rotation pairs
+columns (2i, 2i + 1) of the rotated part's first ``rot_dims`` columns; angles, scores, softmax
+and both norms are 32-bit.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tokenomos_b200 import ops
+from tokenomos_b200.parts.contract import LatentKV, StepContext
+from tokenomos_b200.parts.linear import Linear
+from tokenomos_b200.parts.registry import DEFAULT_TUNING, Runtime, Tuning, register
+from tokenomos_b200.parts.rope import Rotary
+
+
+class LatentAttention:
+    capture_safe = True
+
+    def __init__(self, down: Linear, uq: Linear, uk: torch.Tensor, uv: torch.Tensor, o: Linear,
+                 q_norm: torch.Tensor, kv_norm: torch.Tensor, eps: float, heads: int, dim: int, rot_dim: int,
+                 v_dim: int, q_rank: int, kv_rank: int, freq: torch.Tensor, window: int | None, scale: float,
+                 gated: bool, tuning: Tuning = DEFAULT_TUNING):
+        """``down``: the projections that read the layer's input, fused: q latent, kv latent, the
+        rotated key part, then (``gated``) one gate row per head. ``uk`` [heads * dim, kv_rank],
+        ``uv`` [heads * v_dim, kv_rank] as stored. ``freq``: float32 [rot_dims / 2]."""
+        self.down, self.uq, self.o = down, uq, o
+        self.heads, self.dim, self.rot_dim, self.v_dim = heads, dim, rot_dim, v_dim
+        self.q_rank, self.kv_rank = q_rank, kv_rank
+        self.eps, self.window, self.scale, self.gated = float(eps), window, float(scale), bool(gated)
+        self.q_norm, self.kv_norm = q_norm.float().contiguous(), kv_norm.float().contiguous()
+        self.freq = freq
+        self.tuning = tuning
+        if kv_rank > ops.ATTENTION_LATENT_MAX_RANK:
+            raise ValueError(f"latent attention: a latent of {kv_rank} is above the "
+                             f"{ops.ATTENTION_LATENT_MAX_RANK} the attention kernel takes")
+        if uq.out_features != heads * (dim + rot_dim) or uq.in_features != q_rank:
+            raise ValueError("latent attention: the query up-projection does not match the head sizes")
+        need = q_rank + kv_rank + rot_dim + (heads if gated else 0)
+        if down.out_features < need:
+            raise ValueError("latent attention: the fused down-projection is too narrow")
+        # per head, as the batched products read them: W_uk[h]^T as [kv_rank, dim] rows, W_uv[h] [v_dim, kv_rank]
+        self.uk_t = uk.view(heads, dim, kv_rank).transpose(1, 2).contiguous()
+        self.uv = uv.view(heads, v_dim, kv_rank).contiguous()
+        if o.in_features != heads * v_dim:
+            raise ValueError("latent attention: the output projection does not match the value heads")
+
+    def state_specs(self) -> dict:
+        return {"kv": LatentKV(self.kv_rank + self.rot_dim, self.window)}
+
+    def _batched(self, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """``out[h] = a[h] @ w[h].T``: the library's batched product in 16 bits, the CUDA-core one in 32."""
+        if a.dtype == torch.float32:
+            return ops.gemm_batched(a, w)
+        return torch.bmm(a, w.transpose(1, 2))
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
+        T, H = x.shape[0], self.heads
+        cache = ctx.states[(call, "kv")]
+        table = ctx.block_tables[ctx.state_groups[(call, "kv")]]
+        proj = self.down(x)
+        cq = ops.latent_prepare(proj, self.q_norm, self.kv_norm, self.eps, self.freq, ctx.positions, ctx.tok_seq,
+                                table, cache, self.q_rank, self.kv_rank, self.rot_dim)
+        q = self.uq(cq)
+        ops.latent_rotate_q(q, self.freq, ctx.positions, H, self.dim, self.rot_dim)
+        q_nope = q.view(T, H, self.dim + self.rot_dim)[:, :, :self.dim].transpose(0, 1)      # [H, T, dim]
+        q_lat = self._batched(q_nope, self.uk_t)                                             # [H, T, kv_rank]
+        per_tile = max(1, ops.attention_latent_rows() // H)
+        _, tok0, _, ntok = ctx.tiles(per_tile)
+        lat = ops.attention_latent(q_lat, q, cache, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile, H,
+                                   self.dim, self.rot_dim, self.window, self.scale)           # [H, T, kv_rank]
+        heads_out = self._batched(lat, self.uv)                                              # [H, T, v_dim]
+        n = self.q_rank + self.kv_rank + self.rot_dim
+        out = ops.head_gate_transpose(heads_out, proj[:, n:n + H] if self.gated else None)   # [T, H, v_dim]
+        return self.o(out.view(T, H * self.v_dim))
+
+
+@register("mixer", "latent_attention")
+def build_latent_attention(params: dict, tensors: dict, rt: Runtime) -> LatentAttention:
+    mats = [tensors["dq"], tensors["dkv"]]
+    gated = "gate" in tensors
+    if gated:
+        g = tensors["gate"]
+        pad = -g.shape[0] % 8              # whole 16-byte chunks of the output row
+        mats.append(torch.cat((g, g.new_zeros(pad, g.shape[1]))) if pad else g)
+    rot = params["rot"]
+    freqs, _ = Rotary.table(rot["dims"], float(rot["base"]), None)
+    freq = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(rt.device).contiguous()
+    return LatentAttention(
+        Linear.fused(mats, tuning=rt.tuning), Linear(tensors["uq"], tuning=rt.tuning), tensors["uk"],
+        tensors["uv"], Linear(tensors["o"], tuning=rt.tuning), tensors["dq_norm"], tensors["dkv_norm"],
+        params["eps"], params["heads"], params["dim"], params["rot_dim"], params["v_dim"], params["q_rank"],
+        params["kv_rank"], freq, params.get("window"), params["scale"], gated, rt.tuning)

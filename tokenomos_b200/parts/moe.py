@@ -1,0 +1,70 @@
+"""Mixture of experts feed-forward.
+
+    z = W_router h (32-bit);  s = softmax(z);  the ``top`` experts of the largest s
+    w_k = s_k / (sum of the chosen s + 1e-20) * scale
+    out = sum_k w_k * expert_k(h)  [+ sigmoid(W_sg h) * shared(h)]
+    expert(h) = W_down act(W_up h),  act(v) = relu(v)^2     (no biases)
+
+The router (and the shared expert's gate row, appended to it) is a 32-bit matrix in any model.
+The (token, expert) pairs of a step are sorted by expert on the device into blocks of whole
+tiles, the experts run as two grouped products over that layout (the first gathers its input
+rows and applies the activation), and one kernel combines the outputs per token in 32-bit; the
+launches are the same whatever the routing, so a step can be recorded.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from tokenomos_b200 import ops
+from tokenomos_b200.parts.linear import Linear
+from tokenomos_b200.parts.registry import Runtime, register
+
+
+class RoutedExperts:
+    capture_safe = True
+
+    def __init__(self, router: Linear, up: torch.Tensor, down: torch.Tensor, top: int, scale: float,
+                 shared_up: Linear | None = None, shared_down: Linear | None = None, shared_gate: bool = False):
+        """``up`` [E, ff, width], ``down`` [E, width, ff]; ``router`` [E (+ 1 if ``shared_gate``), width]
+        in float32."""
+        self.router, self.up, self.down = router, up.contiguous(), down.contiguous()
+        self.experts, self.ff, self.width = up.shape
+        self.top, self.scale = int(top), float(scale)
+        if not 1 <= self.top <= self.experts:
+            raise ValueError(f"mixture of experts: {self.top} of {self.experts} experts per token")
+        if tuple(down.shape) != (self.experts, self.width, self.ff):
+            raise ValueError("mixture of experts: down projections do not match the up projections")
+        if (shared_up is None) != (shared_down is None) or (shared_gate and shared_up is None):
+            raise ValueError("mixture of experts: a shared expert has both projections; its gate needs it")
+        self.shared_up, self.shared_down, self.shared_gate = shared_up, shared_down, bool(shared_gate)
+        if router.out_features != self.experts + (1 if shared_gate else 0):
+            raise ValueError("mixture of experts: the router does not match the expert count")
+        self.tile = ops.gemm_grouped_tile()
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        z = self.router(x, out_dtype=torch.float32)
+        idx, w, gate = ops.moe_route(z, self.experts, self.top, self.scale, self.shared_gate)
+        row_token, pair_row, tile_expert = ops.moe_sort(idx, self.experts, self.tile)
+        rows = row_token.numel()
+        act = ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, act=True)
+        y = ops.gemm_grouped(act, self.down, tile_expert, None, rows)
+        shared = None
+        if self.shared_up is not None:
+            shared = self.shared_down(ops.relu2(self.shared_up(x)))
+        return ops.moe_combine(y, pair_row, w, shared, gate)
+
+
+@register("feed_forward", "relu2_moe")
+def build_routed_experts(params: dict, tensors: dict, rt: Runtime) -> RoutedExperts:
+    n = params["experts"]
+    up = torch.stack([tensors[f"e{i}.up"] for i in range(n)])
+    down = torch.stack([tensors[f"e{i}.down"] for i in range(n)])
+    rows = [tensors["router"].float()]
+    gate = tensors.get("shared_gate")
+    if gate is not None:
+        rows.append(gate.float().reshape(1, -1))
+    router = Linear(torch.cat(rows), tuning=rt.tuning)
+    shared_up = Linear(tensors["shared_up"], tuning=rt.tuning) if "shared_up" in tensors else None
+    shared_down = Linear(tensors["shared_down"], tuning=rt.tuning) if "shared_down" in tensors else None
+    return RoutedExperts(router, up, down, params["top"], params["scale"], shared_up, shared_down, gate is not None)

@@ -110,6 +110,7 @@ MIXERS: dict[str, Builder] = {}
 FEED_FORWARDS: dict[str, Builder] = {}
 NORMS: dict[str, Builder] = {}
 POSITIONS: dict[str, Builder] = {}
+EMBEDDINGS: dict[str, Builder] = {}
 BLOCKS: dict[str, Callable] = {}
 
 _FAMILIES = {
@@ -117,6 +118,7 @@ _FAMILIES = {
     "feed_forward": FEED_FORWARDS,
     "norm": NORMS,
     "position": POSITIONS,
+    "embedding": EMBEDDINGS,
     "block": BLOCKS,
 }
 

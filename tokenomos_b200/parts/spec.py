@@ -97,10 +97,15 @@ class ModelSpec:
     suppress: tuple[int, ...] = ()
     # tensors of the stack itself (not of a block), by the name ``StreamAdd.tensor`` uses
     extras: tuple[tuple[str, TensorDecl], ...] = ()
+    # a part of the ``embedding`` family that makes the rows the layer list starts from (None: a
+    # plain gather of ``embedding``'s rows); its tensors may name the embedding table again
+    embedder: PartSpec | None = None
 
     def tensor_decls(self) -> list[TensorDecl]:
         """Every tensor the model reads, in a fixed order (the order random weights are drawn)."""
         out = [self.embedding]
+        if self.embedder is not None:
+            out.extend(self.embedder.tensors.values())
         for block in self.blocks:
             for part in block.parts.values():
                 if part is not None:
