@@ -1038,6 +1038,208 @@ def design_kernels(z: dict, pk: dict) -> list[dict]:
     return rows
 
 
+# ---------------------------------------------------------------------------------------------
+# --design laposun: the Laposun decoder beside the closest existing model (Darizen: a 32-bit
+# stream, windowed gated attention) at equal width, head count, feed-forward size and depth
+# ---------------------------------------------------------------------------------------------
+LAPOSUN_SIZES = {
+    # the Laposun side: latent sizes, streams, taps, experts; the Darizen side reads width, heads,
+    # kv_heads, dim, ff, layers, vocab, window
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, layers=8, vocab=65536, window=1024,
+                  rot_dim=64, q_rank=768, kv_rank=512, streams=2, taps=4, experts=32, top=4, expert_ff=1536,
+                  shared_ff=2048),
+    "w1024": dict(width=1024, heads=16, kv_heads=4, dim=64, ff=4608, layers=8, vocab=65536, window=1024,
+                  rot_dim=32, q_rank=384, kv_rank=256, streams=2, taps=4, experts=16, top=2, expert_ff=1536,
+                  shared_ff=1536),
+}
+
+
+def laposun_config(z: dict) -> dict:
+    """Layers alternate between a dense feed-forward and a mixture of experts whose active size
+    (top experts + the shared one) equals the dense one's."""
+    layers = []
+    for i in range(z["layers"]):
+        mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot_dim"], "vdim": z["dim"],
+                 "q_rank": z["q_rank"], "kv_rank": z["kv_rank"], "scale": (z["dim"] + z["rot_dim"]) ** -0.5,
+                 "mask": {"size": z["window"]}, "rot": {"base": 1000000.0, "dims": z["rot_dim"]}}
+        if i % 2 == 0:
+            mlp = {"kind": "dense", "ff": z["ff"]}
+        else:
+            mlp = {"kind": "moe", "expert": {"ff": z["expert_ff"]},
+                   "router": {"experts": z["experts"], "top": z["top"], "scale": 1.0}, "shared": {"ff": z["shared_ff"]}}
+        layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+    return {"architecture": "Laposun", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "streams": z["streams"], "canon": {"taps": z["taps"]},
+            "embedding": {"bigram": {"buckets": 100003, "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers}
+
+
+def laposun_prefill_flops(z: dict, tokens: int) -> float:
+    """Multiply-adds times two of one prompt of ``tokens`` tokens as this engine computes it."""
+    W, H, D, Dr, R, Rq = z["width"], z["heads"], z["dim"], z["rot_dim"], z["kv_rank"], z["q_rank"]
+    visible = sum(min(i + 1, z["window"]) for i in range(tokens))
+    per_tok = W * (Rq + R + Dr + H) + Rq * H * (D + Dr) + 2 * H * D * R + H * D * W
+    flops = 0.0
+    for i in range(z["layers"]):
+        ff = 3 * W * z["ff"] if i % 2 == 0 else 2 * W * (z["top"] * z["expert_ff"] + z["shared_ff"]) + W * z["experts"]
+        flops += 2.0 * tokens * (per_tok + ff) + 2.0 * visible * H * (2 * R + Dr)
+    return flops + 2.0 * z["vocab"] * W
+
+
+def laposun_kernels(z: dict, pk: dict) -> list[dict]:
+    """Each kernel of the Laposun path beside the kernel of the closest model that does the like
+    work, on the shapes of a 2,048-token prompt portion (or 64 decoded tokens behind 2,048
+    positions), L2 flushed before every launch, CUDA events around the launches, median of 20.
+    ``frac``: bytes over time against the measured copy bandwidth, or flops over time against the
+    measured bf16 rate."""
+    import torch
+    import torch.nn.functional as F
+
+    from tokenomos_b200 import ops
+    from tokenomos_b200.parts.rope import Rotary
+
+    bf, dev = torch.bfloat16, "cuda"
+    T, W, H, G, D, P, win = 2048, z["width"], z["heads"], z["kv_heads"], z["dim"], 16, z["window"]
+    Dr, R, Rq, S, taps = z["rot_dim"], z["kv_rank"], z["q_rank"], z["streams"], z["taps"]
+    flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
+    rows = []
+
+    def add(name, ours_us, theirs_us, ours_work, theirs_work, unit, like):
+        peak = pk["hbm_gbs"] * 1e3 if unit == "bytes" else pk["bf16_tflops"] * 1e6       # per microsecond
+        fo = ours_work / ours_us / peak
+        row = {"kernel": name, "like": like, "laposun_us": round(ours_us, 1), "laposun_frac": round(fo, 3)}
+        if theirs_us is not None:
+            ft = theirs_work / theirs_us / peak
+            row.update(like_us=round(theirs_us, 1), like_frac=round(ft, 3), times_further_from_roofline=round(ft / fo, 2))
+        rows.append(row)
+
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    zero1 = torch.zeros(1, dtype=torch.int32, device=dev)
+    one1 = torch.ones(1, dtype=torch.int32, device=dev)
+
+    # the stream: write of the sublayer before + read + norm + input convolution
+    streams = torch.randn(T, S * W, device=dev)
+    y = torch.randn(T, W, device=dev).to(bf)
+    mix, ow, iw = torch.eye(S, device=dev).reshape(-1).contiguous(), torch.ones(S, device=dev), torch.ones(S, device=dev)
+    nw = torch.ones(W, device=dev)
+    tp = torch.randn(W, taps, device=dev) * 0.1
+    state = torch.zeros(2, taps - 1, W, device=dev)
+    tile = 16
+    n_t = T // tile
+    tiles = (torch.zeros(n_t, dtype=torch.int32, device=dev), torch.arange(0, T, tile, dtype=torch.int32, device=dev),
+             torch.arange(0, T, tile, dtype=torch.int32, device=dev), torch.full((n_t,), tile, dtype=torch.int32, device=dev))
+
+    def read():
+        h = ops.hc_mix_norm(streams, y, mix, ow, iw, nw, 1e-6, S, bf, True)
+        return ops.canon_conv(h, tp, state, cu, zero1, one1, tiles, bf)
+
+    res32 = torch.randn(T, W, device=dev)
+    add("connections + norm + input conv", _timed_us(read, flush),
+        _timed_us(lambda: ops.stream32_add_norm(res32, y, nw, 1e-6), flush),
+        T * W * (8 * S + 2 + 2), T * W * (4 + 2 + 4 + 2), "bytes", "Darizen: residual add + norm")
+
+    # embedding
+    ids = torch.randint(0, z["vocab"], (T,), dtype=torch.int32, device=dev)
+    table = torch.randn(z["vocab"], W, device=dev).to(bf)
+    big = torch.randn(100004, W, device=dev).to(bf)
+    prev = torch.zeros(2, 1, dtype=torch.int32, device=dev)
+    add("hashed bigram embedding + norm",
+        _timed_us(lambda: ops.embed_bigram_norm(table, big, nw, 1e-6, ids, None, seq, cu, zero1, one1, prev, S,
+                                                100003, 1000003, 31), flush),
+        _timed_us(lambda: ops.gather_rows(table, ids), flush), T * W * (4 + 4 * S), T * W * 4, "bytes", "row gather")
+
+    # latent norms + rotation + cache write
+    pages = T // P + 1
+    cache = torch.zeros(pages, P, R + Dr, dtype=bf, device=dev)
+    tbl = torch.arange(1, pages, dtype=torch.int32, device=dev).view(1, -1)
+    proj = torch.randn(T, Rq + R + Dr + 16, device=dev).to(bf)
+    freqs, _ = Rotary.table(Dr, 1e6, None)
+    freq = torch.tensor(freqs, dtype=torch.float64).float().to(dev)
+    pool = torch.zeros(pages, 2, G, P, D, dtype=bf, device=dev)
+    qkv = torch.randn(T, (H + 2 * G) * D, device=dev).to(bf)
+    rot = Rotary(D, D, 1e6, "half", {"kind": "linear", "factor": 8.0}, dev)
+    add("latent norms + rotation + cache write",
+        _timed_us(lambda: ops.latent_prepare(proj, nw[:Rq].contiguous(), nw[:R].contiguous(), 1e-6, freq, pos, seq, tbl,
+                                             cache, Rq, R, Dr), flush),
+        _timed_us(lambda: ops.rotary_write(qkv, pool, rot.freq, 1.0, pos, seq, tbl, H, G, D, D, P, False, False), flush),
+        T * (Rq + R + Dr) * 4, T * (H + 2 * G) * D * 4, "bytes", "Darizen: rotation + cache write")
+
+    # prompt attention
+    ops.latent_prepare(proj, nw[:Rq].contiguous(), nw[:R].contiguous(), 1e-6, freq, pos, seq, tbl, cache, Rq, R, Dr)
+    q = torch.randn(T, H * (D + Dr), device=dev).to(bf) * 0.1
+    q_lat = torch.randn(H, T, R, device=dev).to(bf) * 0.1
+    visible = sum(min(i + 1, win) for i in range(T))
+    qd = ops.rotary_write(qkv, pool, rot.freq, 1.0, pos, seq, tbl, H, G, D, D, P, False, False)
+    outd = torch.empty_like(qd)
+    gate_e = torch.randn(T, H * D, device=dev).to(bf)
+    if ops.attention_prefill_tc_supported(H, G, D, bf):
+        per_d = ops.attention_prefill_tc_tokens(H, G)
+        t0d = torch.arange(0, T, per_d, dtype=torch.int32, device=dev)
+        theirs = _timed_us(lambda: ops.attention_prefill_tc(qd, pool, outd, pos, seq, tbl, t0d, torch.full_like(t0d, per_d),
+                                                            win, D ** -0.5, gate_e, 1, 4, True, True), flush)
+    else:
+        per_d = ops.attention_prefill_mma_tokens(H, G)
+        t0d = torch.arange(0, T, per_d, dtype=torch.int32, device=dev)
+        theirs = _timed_us(lambda: ops.attention_prefill_mma(qd, pool, outd, pos, seq, tbl, t0d, torch.full_like(t0d, per_d),
+                                                             win, D ** -0.5, gate_e, 4, True, True), flush)
+    per = ops.attention_latent_tokens(H, D, R, Dr, bf)
+    t0 = torch.arange(0, T, per, dtype=torch.int32, device=dev)
+    nt = torch.full_like(t0, per)
+    add("prompt attention over the latent cache",
+        _timed_us(lambda: ops.attention_latent(q_lat, q, cache, pos, seq, tbl, t0, nt, per, H, D, Dr, win, 0.1), flush, reps=5),
+        theirs, 2.0 * visible * H * (2 * R + Dr), 4.0 * visible * H * D, "flops", "Darizen: prompt attention")
+
+    # decode attention: 64 sequences of T cached positions (sharing the pages: the bytes are read per sequence)
+    B = 64
+    dpos = torch.full((B,), T - 1, dtype=torch.int32, device=dev)
+    dseq = torch.arange(B, dtype=torch.int32, device=dev)
+    dtbl = tbl.expand(B, -1).contiguous()
+    keys = min(T, win)
+    dq, dq_lat = q[:B].contiguous(), q_lat[:, :B].contiguous()
+    t01 = torch.arange(B, dtype=torch.int32, device=dev)
+    nt1 = torch.ones_like(t01)
+    dqd, doutd = qd[:B].contiguous(), torch.empty_like(qd[:B])
+    add("decode attention over the latent cache, 64 tokens",
+        _timed_us(lambda: ops.attention_latent(dq_lat, dq, cache, dpos, dseq, dtbl, t01, nt1, per, H, D, Dr, win, 0.1),
+                  flush),
+        _timed_us(lambda: ops.attention_decode_mma(dqd, pool, doutd, dpos, dseq, dtbl, None, win, D ** -0.5, 2,
+                                                   gate_e[:B], 4, True, True), flush),
+        B * keys * (R + Dr) * 2, B * G * keys * D * 2 * 2, "bytes", "Darizen: decode attention")
+
+    # the experts' two products (tokens x top rows through [ff, width] and back) beside the library's
+    # product of a dense feed-forward of equal flops
+    E, top, ff = z["experts"], z["top"], z["expert_ff"]
+    x = torch.randn(T, W, device=dev).to(bf)
+    up = torch.randn(E, ff, W, device=dev).to(bf) * 0.02
+    down = torch.randn(E, W, ff, device=dev).to(bf) * 0.02
+    logits = torch.randn(T, E + 1, device=dev)
+    idx, wgt, gate = ops.moe_route(logits, E, top, 1.0, True)
+    tile_rows = ops.gemm_grouped_tile()
+    row_token, pair_row, tile_expert = ops.moe_sort(idx, E, tile_rows)
+    n_rows = row_token.numel()
+
+    def experts():
+        a = ops.gemm_grouped(x, up, tile_expert, row_token, n_rows, act=True)
+        return ops.gemm_grouped(a, down, tile_expert, None, n_rows)
+
+    wd = torch.randn(top * ff, W, device=dev).to(bf) * 0.02
+    wd2 = torch.randn(W, top * ff, device=dev).to(bf) * 0.02
+    add("experts: two grouped products", _timed_us(experts, flush, reps=5),
+        _timed_us(lambda: F.linear(F.linear(x, wd), wd2), flush), 4.0 * T * top * ff * W, 4.0 * T * top * ff * W, "flops",
+        "library product of equal flops")
+    yy = experts()
+    shared = torch.randn(T, W, device=dev).to(bf)
+
+    def routing():
+        i2, w2, g2 = ops.moe_route(logits, E, top, 1.0, True)
+        r2, p2, t2 = ops.moe_sort(i2, E, tile_rows)
+        return ops.moe_combine(yy, p2, w2, shared, g2)
+
+    add("routing + sort + combination", _timed_us(routing, flush), None, T * W * 2 * (top + 2), 0, "bytes", "none")
+    return rows
+
+
 def run_design(name: str, args, warmup: int) -> int:
     """``--design darizen``: decode (batch 8 and 64) and prefill (2,048 tokens) throughput of
     Darizen stacks at a few real layer sizes, beside the LFM3 stack of sliding-window attention
@@ -1050,13 +1252,18 @@ def run_design(name: str, args, warmup: int) -> int:
     from tokenomos_b200.weights import write_model_folder
 
     pk = peaks()
-    for size, z in DESIGN_SIZES.items():
+    sizes = LAPOSUN_SIZES if name == "laposun" else DESIGN_SIZES
+    for size, z in sizes.items():
+        if getattr(args, "design_size", None) and size != args.design_size:
+            continue
         line = {"design": name, "size": size, "sizes": z, "dtype": "bf16",
                 "data": "synthetic token ids, random-init weights N(0, 0.02)"}
-        for arm, config in (("darizen", darizen_config(z)), ("lfm3", lfm3_like_config(z))):
+        arms = ((("laposun", laposun_config(z)), ("darizen", darizen_config(z))) if name == "laposun" else
+                (("darizen", darizen_config(z)), ("lfm3", lfm3_like_config(z))))
+        for arm, config in arms:
             with tempfile.TemporaryDirectory(prefix="tokenomos_b200_design_") as tmp:
                 folder = Path(tmp) / arm
-                if arm == "darizen":
+                if arm != "lfm3":
                     write_model_folder(folder, config, 0, 0.02, 0.0, torch.bfloat16)
                 else:
                     write_folder(folder, z["layers"], config)
@@ -1068,12 +1275,13 @@ def run_design(name: str, args, warmup: int) -> int:
                 res[f"decode_b{batch}"] = {"tok_s": round(d["tok_s"], 1), "ms_per_step": round(d["ms_per_step"], 4),
                                            "launches": d["launches_per_step"]}
             pf = device_prefill(model, cfg, args.page)
+            flops = laposun_prefill_flops(z, pf["tokens"]) if arm == "laposun" else pf["flops"]
             res["prefill_2048"] = {"tok_s": round(pf["tok_s"], 1), "ms": round(pf["ms"], 3),
-                                   "frac": round(pf["flops"] / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+                                   "frac": round(flops / (pf["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
             line[arm] = res
             del model
             torch.cuda.empty_cache()
-        line["kernels"] = design_kernels(z, pk)
+        line["kernels"] = laposun_kernels(z, pk) if name == "laposun" else design_kernels(z, pk)
         print(json.dumps(line), flush=True)
     return 0
 
@@ -1102,8 +1310,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--trace", default=None,
                     help="--workload: write one JSON record per step of an extra pass to this file")
-    ap.add_argument("--design", default=None, choices=["darizen"],
-                    help="the named design beside the closest LFM3 configuration at equal sizes instead")
+    ap.add_argument("--design", default=None, choices=["darizen", "laposun"],
+                    help="the named design beside the closest existing model at equal sizes instead (darizen beside "
+                         "LFM3, laposun beside darizen)")
+    ap.add_argument("--design-size", default=None, help="only this size of the design's table")
     ap.add_argument("--sweep", action="store_true",
                     help="decode and prefill at other batch sizes and context lengths instead")
     args = ap.parse_args()

@@ -98,7 +98,10 @@ def make_tensors(config: dict, seed: int) -> dict[str, torch.Tensor]:
     tensors = random_tensors(spec.tensor_decls(), seed, std=1.0)
     S = config.get("streams") or 1
     out = {}
+    noise = torch.Generator().manual_seed(seed + 1000)
     for name, t in tensors.items():
+        if ".hc" in name or "norm" in name:          # (the random-weights mode draws these as ones)
+            t = torch.randn(t.shape, generator=noise)
         if name.endswith((".hc1.in", ".hc2.in")):
             t = 1.0 / S + 0.3 * t
         elif name.endswith((".hc1.out", ".hc2.out")):
@@ -435,7 +438,7 @@ class LatentSequence:
         qq = q[a:b].reshape(b - a, -1).to(self.dtype).cuda().contiguous()
         ops.latent_rotate_q(qq, self.freq, ctx.positions, self.H, self.D, self.Dr)
         q_lat = q[a:b, :, :self.R].transpose(0, 1).to(self.dtype).cuda().contiguous()       # D >= R in these tests
-        per_tile = max(1, ops.attention_latent_rows() // self.H)
+        per_tile = ops.attention_latent_tokens(self.H, self.D, self.R, self.Dr, self.dtype)
         _, tok0, _, ntok = ctx.tiles(per_tile)
         out = ops.attention_latent(q_lat, qq, cache, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
                                    self.H, self.D, self.Dr, window, scale)
@@ -465,6 +468,8 @@ def plain_latent_scores(proj, q, R, Dr, rot, base, window, scale, eps=1e-6):
 @pytest.mark.parametrize("how", ["whole", "decoded", "portions"])
 @pytest.mark.parametrize("case", [dict(H=3, D=20, Dr=6, R=20, rot=4, page=4, window=9),
                                   dict(H=16, D=64, Dr=32, R=64, rot=32, page=16, window=33),
+                                  dict(H=6, D=96, Dr=16, R=96, rot=16, page=8, window=70),
+                                  dict(H=40, D=32, Dr=16, R=32, rot=8, page=4, window=20),
                                   dict(H=5, D=40, Dr=8, R=40, rot=8, page=8, window=None),
                                   dict(H=2, D=24, Dr=2, R=24, rot=2, page=4, window=1)])
 def test_latent_cache_and_attention_with_one_loud_key(case, dtype, how):
@@ -513,6 +518,32 @@ def test_batched_and_grouped_products():
     strided = torch.randn(70, 5, 40, generator=g).cuda()[:, :, :24].transpose(0, 1)      # [5, 70, 24], rows 200 apart
     got = ops.gemm_batched(strided, w)
     assert (got - torch.einsum("gmk,gnk->gmn", strided.double(), w.double()).float()).abs().max() < 1e-4
+    # bfloat16 in whole 16-byte chunks: the tensor-core form; rows, columns and K that fill no tile
+    for G, M, N, K in ((3, 70, 136, 72), (2, 1, 8, 8), (1, 200, 264, 40)):
+        a16 = torch.randn(G, M, K, generator=g).to(torch.bfloat16).cuda()
+        w16 = torch.randn(G, N, K, generator=g).to(torch.bfloat16).cuda()
+        want = torch.einsum("gmk,gnk->gmn", a16.double(), w16.double())
+        got = ops.gemm_batched(a16, w16).double()
+        assert (got - want).abs().max() < 1e-2 * want.abs().max()
+    # grouped, with gathered rows, zero rows and unused tiles
+    tile = ops.gemm_grouped_tile()
+    for dtype in (torch.float32, torch.bfloat16):
+        x = torch.randn(50, 64, generator=g).to(torch.bfloat16).to(dtype).cuda()
+        w3 = torch.randn(3, 72, 64, generator=g).to(torch.bfloat16).to(dtype).cuda()
+        rows = 4 * tile
+        row_index = torch.full((rows,), -1, dtype=torch.int32)
+        row_index[:5] = torch.tensor([7, 7, 0, 49, 3])
+        row_index[tile:tile + 2] = torch.tensor([1, 2])
+        row_index[3 * tile:3 * tile + tile] = torch.arange(tile) % 50
+        groups = torch.tensor([2, 0, -1, 1], dtype=torch.int32)
+        got = ops.gemm_grouped(x, w3, groups.cuda(), row_index.cuda(), rows, act=True).double().cpu()
+        for t, grp in enumerate(groups.tolist()):
+            if grp < 0:
+                continue
+            idx = row_index[t * tile:(t + 1) * tile]
+            src = torch.where(idx[:, None] >= 0, x.double().cpu()[idx.clamp(min=0).long()], torch.zeros(1, dtype=torch.float64))
+            want = torch.relu(src @ w3[grp].double().cpu().T) ** 2
+            assert (got[t * tile:(t + 1) * tile] - want).abs().max() < (1e-4 if dtype == torch.float32 else 2e-2) * want.abs().max()
 
 
 @pytest.mark.gpu

@@ -343,3 +343,270 @@ TK_API int tk_head_gate_transpose(const void* x, const void* g, int64_t g_stride
     TK_CHECK_LAUNCH("head_gate_transpose");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same attention on the tensor cores for bfloat16 (mma.sync m16n8k16, 32-bit scores, softmax
+// and sums). A CTA of 8 warps takes 32 rows (tokens x heads of one tile) and walks the keys 64 at
+// a time through a two-stage cp.async pipeline; a key row [c | k_rot] is staged once and serves
+// as the key (all of it) and as the value (its first R columns, read transposed by ldmatrix).
+// Scores: warp (row group, key quarter) forms S[16 x 16] over the whole row; the row maxima meet
+// in shared memory; P goes to shared memory in 16 bits. Output: warp (row group, column quarter)
+// accumulates O[16 x R/4]. Needs R % 32 == 0, R <= 512, Dr % 16 == 0, D % 8 == 0.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr int AM = 32, AN = 64, A_THREADS = 256, PLD = AN + 8;
+
+__device__ __forceinline__ void a_cp_async16(void* dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void a_ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void a_ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void a_mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+}  // namespace
+
+template <int MAXNB>       // n8 blocks of the output a warp may hold: R / 32 <= MAXNB
+__global__ void __launch_bounds__(A_THREADS, 1)
+attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const __nv_bfloat16* cache,
+                       __nv_bfloat16* out, const int* positions, const int* tok_seq, const int* block_table,
+                       int bt_stride, const int* tile_tok0, const int* tile_ntok, int tokens, int H, int D, int R,
+                       int Dr, int P, int window, float scale, int heads_per_chunk) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int DK = R + Dr, KLD = DK + 8;
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [AM][KLD]
+    __nv_bfloat16* Ks = Qs + AM * KLD;                                       // [2][AN][KLD]
+    __nv_bfloat16* Ps = Ks + 2 * AN * KLD;                                   // [AM][PLD]
+    float* red_max = reinterpret_cast<float*>(Ps + AM * PLD);                // [2 row groups][4][16]
+    float* red_sum = red_max + 128;                                          // [2][4][16]
+    __shared__ int row_pos[AM];
+
+    const int g0 = blockIdx.y * heads_per_chunk;
+    const int gh = min(heads_per_chunk, H - g0);
+    const int tok0 = tile_tok0[blockIdx.x];
+    const int ntok = tile_ntok[blockIdx.x];
+    if (ntok <= 0) return;
+    const int rows = ntok * gh;
+    const int seq = tok_seq[tok0];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rg = warp >> 2, wq = warp & 3;
+    const int chunks = DK / 8;
+
+    if (tid < AM) row_pos[tid] = tid < rows ? positions[tok0 + tid / gh] : -1;
+    // the queries: [q in the latent's space | rotated part], rows beyond the tile's are zero
+    for (int c = tid; c < AM * chunks; c += A_THREADS) {
+        const int r = c / chunks, ch = c % chunks;
+        const bool valid = r < rows;
+        const void* src = q_lat;
+        if (valid) {
+            const int t = tok0 + r / gh, h = g0 + r % gh;
+            src = ch * 8 < R ? (const void*)(q_lat + ((size_t)h * tokens + t) * R + ch * 8)
+                             : (const void*)(q + ((size_t)t * H + h) * (D + Dr) + D + (ch * 8 - R));
+        }
+        a_cp_async16(Qs + r * KLD + ch * 8, src, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    __syncthreads();
+    const int pos_first = row_pos[0];
+    const int pos_last = row_pos[rows - 1];
+    const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    const int n_it = (pos_last - lo) / AN + 1;
+
+    auto load_keys = [&](int it, int stage) {
+        const int key = tid >> 2;
+        const int j = lo + it * AN + key;
+        const bool valid = j <= pos_last;
+        const __nv_bfloat16* src = cache;
+        if (valid) {
+            const int page = TK_PAGE(TK_K_LATENT, block_table[(size_t)seq * bt_stride + j / P]);
+            src = cache + ((size_t)page * P + (j % P)) * DK;
+        }
+        __nv_bfloat16* dst = Ks + ((size_t)stage * AN + key) * KLD;
+        for (int ch = tid & 3; ch < chunks; ch += 4) a_cp_async16(dst + ch * 8, src + ch * 8, valid);
+    };
+    load_keys(0, 0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+
+    const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;
+    const int pos0 = row_pos[r0], pos1 = row_pos[r1];
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    float acc[MAXNB][4];
+#pragma unroll
+    for (int j = 0; j < MAXNB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const int nb = R / 32;                  // n8 blocks of my column quarter
+    const int col0 = wq * (R / 4);
+
+    for (int it = 0; it < n_it; ++it) {
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        if (it + 1 < n_it) load_keys(it + 1, (it + 1) & 1);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        const __nv_bfloat16* ks = Ks + (size_t)(it & 1) * AN * KLD;
+        // ---- scores of my 16 rows against my 16 keys ----
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            const __nv_bfloat16* qa = Qs + (rg * 16 + (lane & 15)) * KLD + (lane >> 4) * 8;
+            const __nv_bfloat16* kb = ks + (wq * 16 + (lane & 7) + (lane >> 4) * 8) * KLD + ((lane >> 3) & 1) * 8;
+            for (int k = 0; k < DK; k += 16) {
+                unsigned a[4], b[4];
+                a_ldmatrix_x4(a, qa + k);
+                a_ldmatrix_x4(b, kb + k);
+                a_mma_bf16(s[0], a, b[0], b[1]);
+                a_mma_bf16(s[1], a, b[2], b[3]);
+            }
+        }
+        const int jbase = lo + it * AN + wq * 16 + (lane & 3) * 2;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int jn = 0; jn < 2; ++jn)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = jbase + jn * 8 + e;
+                const bool v0 = j <= pos0 && (window <= 0 || pos0 - j < window);
+                const bool v1 = j <= pos1 && (window <= 0 || pos1 - j < window);
+                s[jn][e] = v0 ? s[jn][e] * scale : -INFINITY;
+                s[jn][2 + e] = v1 ? s[jn][2 + e] * scale : -INFINITY;
+                mx0 = fmaxf(mx0, s[jn][e]);
+                mx1 = fmaxf(mx1, s[jn][2 + e]);
+            }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        if ((lane & 3) == 0) {
+            red_max[(rg * 4 + wq) * 16 + (lane >> 2)] = mx0;
+            red_max[(rg * 4 + wq) * 16 + (lane >> 2) + 8] = mx1;
+        }
+        __syncthreads();
+        float n0 = m0, n1 = m1;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            n0 = fmaxf(n0, red_max[(rg * 4 + w) * 16 + (lane >> 2)]);
+            n1 = fmaxf(n1, red_max[(rg * 4 + w) * 16 + (lane >> 2) + 8]);
+        }
+        const float s0 = n0 == -INFINITY ? 0.f : n0, s1 = n1 == -INFINITY ? 0.f : n1;
+        const float alpha0 = expf(m0 - s0), alpha1 = expf(m1 - s1);
+        m0 = n0;
+        m1 = n1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int jn = 0; jn < 2; ++jn) {
+            const float p00 = expf(s[jn][0] - s0), p01 = expf(s[jn][1] - s0);
+            const float p10 = expf(s[jn][2] - s1), p11 = expf(s[jn][3] - s1);
+            ps0 += p00 + p01;
+            ps1 += p10 + p11;
+            const int col = wq * 16 + jn * 8 + (lane & 3) * 2;
+            *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * PLD + col) = __floats2bfloat162_rn(p00, p01);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + r1 * PLD + col) = __floats2bfloat162_rn(p10, p11);
+        }
+        l0 = l0 * alpha0 + ps0;             // (my keys' share of the row sums; the quad is summed at the end)
+        l1 = l1 * alpha1 + ps1;
+#pragma unroll
+        for (int j = 0; j < MAXNB; ++j) {
+            acc[j][0] *= alpha0; acc[j][1] *= alpha0;
+            acc[j][2] *= alpha1; acc[j][3] *= alpha1;
+        }
+        __syncthreads();
+        // ---- my 16 rows x my quarter of the latent's columns += P . V ----
+#pragma unroll
+        for (int kk = 0; kk < AN; kk += 16) {
+            unsigned a[4];
+            a_ldmatrix_x4(a, Ps + (rg * 16 + (lane & 15)) * PLD + kk + (lane >> 4) * 8);
+            const __nv_bfloat16* vb = ks + (kk + (lane & 7) + ((lane >> 3) & 1) * 8) * KLD + col0 + (lane >> 4) * 8;
+#pragma unroll
+            for (int jp = 0; jp < (MAXNB + 1) / 2; ++jp) {
+                if (jp * 2 < nb) {
+                    unsigned b[4];
+                    a_ldmatrix_x4_trans(b, vb + jp * 16);
+                    a_mma_bf16(acc[jp * 2], a, b[0], b[1]);
+                    if (jp * 2 + 1 < MAXNB && jp * 2 + 1 < nb) a_mma_bf16(acc[jp * 2 + 1 < MAXNB ? jp * 2 + 1 : 0], a, b[2], b[3]);
+                }
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    // the row sums: over the quad, then over the four key quarters
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    __syncthreads();
+    if ((lane & 3) == 0) {
+        red_sum[(rg * 4 + wq) * 16 + (lane >> 2)] = l0;
+        red_sum[(rg * 4 + wq) * 16 + (lane >> 2) + 8] = l1;
+    }
+    __syncthreads();
+    float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        t0 += red_sum[(rg * 4 + w) * 16 + (lane >> 2)];
+        t1 += red_sum[(rg * 4 + w) * 16 + (lane >> 2) + 8];
+    }
+    const float inv0 = t0 > 0.f ? 1.0f / t0 : 0.f, inv1 = t1 > 0.f ? 1.0f / t1 : 0.f;
+#pragma unroll
+    for (int j = 0; j < MAXNB; ++j) {
+        if (j >= nb) break;
+        const int col = col0 + j * 8 + (lane & 3) * 2;
+        if (r0 < rows) {
+            const int t = tok0 + r0 / gh, h = g0 + r0 % gh;
+            *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)h * tokens + t) * R + col) =
+                __floats2bfloat162_rn(acc[j][0] * inv0, acc[j][1] * inv0);
+        }
+        if (r1 < rows) {
+            const int t = tok0 + r1 / gh, h = g0 + r1 % gh;
+            *reinterpret_cast<__nv_bfloat162*>(out + ((size_t)h * tokens + t) * R + col) =
+                __floats2bfloat162_rn(acc[j][2] * inv1, acc[j][3] * inv1);
+        }
+    }
+}
+
+TK_API int tk_attn_latent_mma_rows() { return AM; }
+
+// 1 when the tensor-core form takes these sizes
+TK_API int tk_attn_latent_mma_supported(int D, int R, int Dr) {
+    return (R % 32 == 0 && R >= 32 && R <= 512 && Dr % 16 == 0 && Dr >= 16 && D % 8 == 0) ? 1 : 0;
+}
+
+TK_API int tk_attn_latent_mma(const void* q_lat, const void* q, const void* cache, void* out, const int* positions,
+                              const int* tok_seq, const int* block_table, int bt_stride, const int* tile_tok0,
+                              const int* tile_ntok, int n_tiles, int tokens_per_tile, int tokens, int H, int D, int R,
+                              int Dr, int P, int window, float scale, cudaStream_t stream) {
+    TK_CHECK_ARG(tk_attn_latent_mma_supported(D, R, Dr), "latent attention (mma): sizes D=%d R=%d Dr=%d", D, R, Dr);
+    TK_CHECK_ARG(H > 0 && P > 0 && n_tiles >= 0 && tokens >= 0, "latent attention (mma): bad counts");
+    TK_CHECK_ARG(tokens_per_tile >= 1 && tokens_per_tile <= AM, "latent attention (mma): %d tokens per tile", tokens_per_tile);
+    if (n_tiles == 0) return 0;
+    const int hpc = min(H, AM / tokens_per_tile);
+    const int KLD = R + Dr + 8;
+    const size_t smem = (size_t)(AM + 2 * AN) * KLD * 2 + (size_t)AM * PLD * 2 + 256 * sizeof(float);
+    dim3 grid(n_tiles, (H + hpc - 1) / hpc);
+#define TK_ALM(NB)                                                                                                 \
+    do {                                                                                                           \
+        cudaFuncSetAttribute(attn_latent_mma_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        tk_launch(attn_latent_mma_kernel<NB>, grid, dim3(A_THREADS), smem, stream, (const __nv_bfloat16*)q_lat,     \
+                  (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, positions, tok_seq,   \
+                  block_table, bt_stride, tile_tok0, tile_ntok, tokens, H, D, R, Dr, P, window, scale, hpc);       \
+    } while (0)
+    const int nb = R / 32;
+    if (nb <= 2) TK_ALM(2);
+    else if (nb <= 4) TK_ALM(4);
+    else if (nb <= 8) TK_ALM(8);
+    else TK_ALM(16);
+#undef TK_ALM
+    TK_CHECK_LAUNCH("attn_latent_mma");
+    return 0;
+}

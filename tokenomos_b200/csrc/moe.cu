@@ -303,3 +303,148 @@ TK_API int tk_relu2(void* x, int64_t n, int dtype, cudaStream_t stream) {
     TK_CHECK_LAUNCH("relu2");
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same product on the tensor cores for bfloat16: mma.sync m16n8k16, 32-bit accumulation, a
+// 64 x 128 tile per CTA (8 warps of 32 x 32), K in steps of 32 through a three-stage cp.async
+// pipeline, operands read with ldmatrix from rows padded to 80 bytes. Gathered rows (a row index
+// of -1, rows beyond M, columns beyond N or K) are zero-filled by the copy itself. Needs K and N
+// in whole 16-byte chunks and 16-byte aligned rows.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr int GM = 64, GN = 128, GK = 32, GLD = 40, GSTAGES = 3, G_THREADS = 256;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+    const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+                 "{%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+}  // namespace
+
+__global__ void __launch_bounds__(G_THREADS)
+gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const int* row_index,
+                        const __nv_bfloat16* __restrict__ W, int64_t ldw, int64_t w_gs, const int* tile_group,
+                        __nv_bfloat16* C, int64_t ldc, int64_t c_gs, int M, int N, int K, int act) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ __align__(16) __nv_bfloat16 As[GSTAGES][GM * GLD];
+    __shared__ __align__(16) __nv_bfloat16 Ws[GSTAGES][GN * GLD];
+    __shared__ int rows_s[GM];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
+    if (tile_group != nullptr) {
+        const int g = tile_group[blockIdx.y];
+        if (g < 0) return;
+        W += (size_t)g * w_gs;
+    } else {
+        A += (size_t)blockIdx.z * a_gs;
+        W += (size_t)blockIdx.z * w_gs;
+        C += (size_t)blockIdx.z * c_gs;
+    }
+    if (tid < GM) {
+        const int m = m0 + tid;
+        rows_s[tid] = m < M ? (row_index != nullptr ? row_index[m] : m) : -1;
+    }
+    __syncthreads();
+    const int a_row = tid >> 2, a_chunk = (tid & 3) * 8;          // one 16-byte chunk of the A tile per thread
+    const int a_src = rows_s[a_row];
+    const int ktiles = (K + GK - 1) / GK;
+    auto load = [&](int kt, int stage) {
+        const int k = kt * GK + a_chunk;
+        const bool av = a_src >= 0 && k < K;
+        cp_async16(&As[stage][a_row * GLD + a_chunk], av ? (const void*)(A + (size_t)a_src * lda + k) : (const void*)A, av);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int r = (tid >> 2) + i * 64;
+            const int n = n0 + r;
+            const bool wv = n < N && k < K;
+            cp_async16(&Ws[stage][r * GLD + a_chunk], wv ? (const void*)(W + (size_t)n * ldw + k) : (const void*)W, wv);
+        }
+    };
+    for (int s = 0; s < GSTAGES - 1; ++s) {
+        if (s < ktiles) load(s, s);
+        cp_async_commit();
+    }
+    const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;
+    float acc[2][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+    for (int kt = 0; kt < ktiles; ++kt) {
+        cp_async_wait<GSTAGES - 2>();
+        __syncthreads();
+        if (kt + GSTAGES - 1 < ktiles) load(kt + GSTAGES - 1, (kt + GSTAGES - 1) % GSTAGES);
+        cp_async_commit();
+        const __nv_bfloat16* as = As[kt % GSTAGES];
+        const __nv_bfloat16* ws = Ws[kt % GSTAGES];
+#pragma unroll
+        for (int kk = 0; kk < GK; kk += 16) {
+            unsigned a[2][4], b[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                ldmatrix_x4(a[i], as + (wm + i * 16 + (lane & 15)) * GLD + kk + (lane >> 4) * 8);
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+                ldmatrix_x4(b[j], ws + (wn + j * 16 + (lane & 7) + (lane >> 4) * 8) * GLD + kk + ((lane >> 3) & 1) * 8);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int m = m0 + wm + i * 16 + (lane >> 2) + half * 8;
+            if (m >= M) continue;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int n = n0 + wn + j * 8 + (lane & 3) * 2;
+                if (n >= N) continue;
+                float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
+                if (act == 1) {
+                    v0 = fmaxf(v0, 0.f); v0 *= v0;
+                    v1 = fmaxf(v1, 0.f); v1 *= v1;
+                }
+                *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + n) = __floats2bfloat162_rn(v0, v1);
+            }
+        }
+    }
+}
+
+TK_API int tk_gemm_grouped_mma(const void* A, int64_t lda, int64_t a_gs, const int* row_index, const void* W,
+                               int64_t ldw, int64_t w_gs, const int* tile_group, void* C, int64_t ldc,
+                               int64_t c_gs, int M, int N, int K, int groups, int act, cudaStream_t stream) {
+    TK_CHECK_ARG(M >= 0 && N > 0 && K > 0 && groups >= 1, "gemm_grouped_mma: bad sizes M=%d N=%d K=%d", M, N, K);
+    TK_CHECK_ARG(K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ldc % 2 == 0 && a_gs % 8 == 0 &&
+                     w_gs % 8 == 0 && c_gs % 2 == 0,
+                 "gemm_grouped_mma: K, N and the strides must be whole 16-byte chunks");
+    TK_CHECK_ARG(((uintptr_t)A % 16) == 0 && ((uintptr_t)W % 16) == 0 && ((uintptr_t)C % 4) == 0,
+                 "gemm_grouped_mma: operands must be 16-byte aligned");
+    TK_CHECK_ARG(act == 0 || act == 1, "gemm_grouped_mma: activation %d", act);
+    if (M == 0) return 0;
+    dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM, tile_group != nullptr ? 1 : groups);
+    tk_launch(gemm_grouped_mma_kernel, grid, dim3(G_THREADS), 0, stream, (const __nv_bfloat16*)A, lda, a_gs, row_index,
+              (const __nv_bfloat16*)W, ldw, w_gs, tile_group, (__nv_bfloat16*)C, ldc, c_gs, M, N, K, act);
+    TK_CHECK_LAUNCH("gemm_grouped_mma");
+    return 0;
+}

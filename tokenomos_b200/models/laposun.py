@@ -24,8 +24,8 @@ Tensor names: ``embed``, ``bigram``, ``embed.norm``, ``final.norm``, and per lay
 from __future__ import annotations
 
 from tokenomos_b200.config.laposun import LaposunConfig
-from tokenomos_b200.parts.spec import (ROLE_EMBEDDING, ROLE_NORM, ROLE_VECTOR, BlockSpec, LayerCall, ModelSpec,
-                                       PartSpec, TensorDecl)
+from tokenomos_b200.parts.spec import (ROLE_EMBEDDING, ROLE_IDENTITY, ROLE_NORM, ROLE_VECTOR, BlockSpec, LayerCall,
+                                       ModelSpec, PartSpec, TensorDecl)
 
 
 class Laposun:
@@ -39,9 +39,10 @@ class Laposun:
         def reader(p: str, q: int) -> PartSpec:
             tensors = {"weight": TensorDecl(f"{p}norm{q}", (d,), ROLE_NORM)}
             if cfg.streams is not None:
-                tensors["in"] = TensorDecl(f"{p}hc{q}.in", (S,), ROLE_VECTOR)
-                tensors["out"] = TensorDecl(f"{p}hc{q}.out", (S,), ROLE_VECTOR)
-                tensors["mix"] = TensorDecl(f"{p}hc{q}.mix", (S, S), ROLE_VECTOR)
+                # (roles: what the random-weights mode draws is the plain residual stream, not zeros)
+                tensors["in"] = TensorDecl(f"{p}hc{q}.in", (S,), ROLE_NORM)
+                tensors["out"] = TensorDecl(f"{p}hc{q}.out", (S,), ROLE_NORM)
+                tensors["mix"] = TensorDecl(f"{p}hc{q}.mix", (S, S), ROLE_IDENTITY)
             if cfg.taps is not None:
                 tensors["taps"] = TensorDecl(f"{p}canon{q}", (d, cfg.taps), ROLE_VECTOR)
             return PartSpec("hyper_norm", {"eps": cfg.norm_eps, "streams": S}, tensors)

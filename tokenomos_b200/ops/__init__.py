@@ -915,6 +915,19 @@ def attention_latent_rows() -> int:
     return _lib.call("tk_attn_latent_rows")
 
 
+def attention_latent_mma_supported(dim: int, rank: int, rot_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core form of the latent attention takes these sizes (else the general
+    kernel does): bfloat16, a latent of a multiple of 32 up to 512, a rotated part of a multiple of 16."""
+    return dtype == torch.bfloat16 and bool(_lib.call("tk_attn_latent_mma_supported", int(dim), int(rank), int(rot_dim)))
+
+
+def attention_latent_tokens(heads: int, dim: int, rank: int, rot_dim: int, dtype: torch.dtype) -> int:
+    """Tokens of one sequence a tile of the latent attention holds (rows of a tile / heads, at least one)."""
+    rows = (_lib.call("tk_attn_latent_mma_rows") if attention_latent_mma_supported(dim, rank, rot_dim, dtype)
+            else _lib.call("tk_attn_latent_rows"))
+    return max(1, rows // heads)
+
+
 ATTENTION_LATENT_MAX_RANK = 512
 
 
@@ -931,6 +944,12 @@ def attention_latent(q_lat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, 
             or q_lat.dtype != q.dtype):
         raise KernelError("attention_latent: q / cache layouts do not match")
     out = torch.empty(H, T, R, dtype=q.dtype, device=q.device)
+    if attention_latent_mma_supported(dim, R, rot_dim, q.dtype) and tokens_per_tile <= _lib.call("tk_attn_latent_mma_rows"):
+        _lib.call("tk_attn_latent_mma", _ptr(q_lat), _ptr(q), _ptr(cache), _ptr(out), _ptr(_i32(positions, "positions")),
+                  _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
+                  _ptr(_i32(tile_tok0, "tile_tok0")), _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(),
+                  int(tokens_per_tile), T, H, dim, R, rot_dim, cache.shape[1], int(window or 0), float(scale), _stream())
+        return out
     _lib.call("tk_attn_latent", _ptr(q_lat), _ptr(q), _ptr(cache), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
               _ptr(_i32(tile_tok0, "tile_tok0")), _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(),
@@ -1000,10 +1019,21 @@ def gemm_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row
     if a.dtype != w.dtype or a.stride(1) != 1 or not w.is_contiguous() or a.shape[1] != K:
         raise KernelError(f"gemm_grouped: a {tuple(a.shape)} {a.dtype} against w {tuple(w.shape)} {w.dtype}")
     out = torch.empty(rows, N, dtype=a.dtype, device=a.device)
+    if _grouped_mma_ok(a, w, N, K):
+        _lib.call("tk_gemm_grouped_mma", _ptr(a), a.stride(0), 0, _ptr(row_index), _ptr(w), K, N * K,
+                  _ptr(_i32(tile_group, "tile_group")), _ptr(out), N, 0, rows, N, K, G, int(bool(act)), _stream())
+        return out
     _lib.call("tk_gemm_grouped_simt", _ptr(a), a.stride(0), 0, _ptr(row_index), _ptr(w), K, N * K,
               _ptr(_i32(tile_group, "tile_group")), _ptr(out), N, 0, rows, N, K, G, int(bool(act)), _dtype_code(a),
               _stream())
     return out
+
+
+def _grouped_mma_ok(a: torch.Tensor, w: torch.Tensor, N: int, K: int) -> bool:
+    """Whether the tensor-core form of the grouped / batched product takes these operands: bfloat16,
+    K, N and the row strides in whole 16-byte chunks, 16-byte aligned."""
+    return (a.dtype == torch.bfloat16 and K % 8 == 0 and N % 8 == 0 and a.stride(-2) % 8 == 0
+            and w.stride(-2) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -1018,6 +1048,11 @@ def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
         out = torch.empty(G, M, N, dtype=a.dtype, device=a.device)
     if out.stride(2) != 1:
         raise KernelError("gemm_batched: out needs contiguous columns")
+    if (_grouped_mma_ok(a, w, N, K) and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and out.stride(1) % 2 == 0
+            and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
+        _lib.call("tk_gemm_grouped_mma", _ptr(a), a.stride(1), a.stride(0), None, _ptr(w), w.stride(1), w.stride(0),
+                  None, _ptr(out), out.stride(1), out.stride(0), M, N, K, G, 0, _stream())
+        return out
     _lib.call("tk_gemm_grouped_simt", _ptr(a), a.stride(1), a.stride(0), None, _ptr(w), w.stride(1), w.stride(0),
               None, _ptr(out), out.stride(1), out.stride(0), M, N, K, G, 0, _dtype_code(a), _stream())
     return out

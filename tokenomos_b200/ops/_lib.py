@@ -76,11 +76,15 @@ _SIGNATURES = {
     "tk_attn_latent_rows": [],
     "tk_attn_latent_max_rank": [],
     "tk_attn_latent": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
+    "tk_attn_latent_mma_rows": [],
+    "tk_attn_latent_mma_supported": [I, I, I],
+    "tk_attn_latent_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "tk_head_gate_transpose": [P, P, L, P, I, I, I, I, P],
     "tk_moe_route": [P, L, I, I, I, F, I, P, P, P, P],
     "tk_moe_sort": [P, I, I, I, I, I, P, P, P, P],
     "tk_gemm_grouped_tile": [],
     "tk_gemm_grouped_simt": [P, L, L, P, P, L, L, P, P, L, L, I, I, I, I, I, I, P],
+    "tk_gemm_grouped_mma": [P, L, L, P, P, L, L, P, P, L, L, I, I, I, I, I, P],
     "tk_moe_combine": [P, P, P, P, P, P, I, I, I, I, P],
     "tk_relu2": [P, L, I, P],
 }
@@ -132,7 +136,8 @@ def calls() -> int:
 _QUERIES = {"tk_check_device", "tk_built_for", "tk_set_pdl", "tk_checks_enabled", "tk_checks_set_bounds", "tk_checks_status", "tk_attn_generic_rows", "tk_conv_min_tile",
             "tk_attn_mma_supported", "tk_attn_decode_fused_supported", "tk_attn_decode_fused_max_splits", "tk_attn_prefill_mma_tokens", "tk_attn_prefill_tc_supported",
             "tk_attn_prefill_tc_tokens", "tk_attn_prefill_tc_status", "tk_gemm_tc_status", "tk_sample_status",
-            "tk_attn_latent_rows", "tk_attn_latent_max_rank", "tk_gemm_grouped_tile"}
+            "tk_attn_latent_rows", "tk_attn_latent_max_rank", "tk_gemm_grouped_tile", "tk_attn_latent_mma_rows",
+            "tk_attn_latent_mma_supported"}
 
 
 _fns: dict = {}

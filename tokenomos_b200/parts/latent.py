@@ -76,7 +76,7 @@ class LatentAttention:
         ops.latent_rotate_q(q, self.freq, ctx.positions, H, self.dim, self.rot_dim)
         q_nope = q.view(T, H, self.dim + self.rot_dim)[:, :, :self.dim].transpose(0, 1)      # [H, T, dim]
         q_lat = self._batched(q_nope, self.uk_t)                                             # [H, T, kv_rank]
-        per_tile = max(1, ops.attention_latent_rows() // H)
+        per_tile = ops.attention_latent_tokens(H, self.dim, self.kv_rank, self.rot_dim, q.dtype)
         _, tok0, _, ntok = ctx.tiles(per_tile)
         lat = ops.attention_latent(q_lat, q, cache, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile, H,
                                    self.dim, self.rot_dim, self.window, self.scale)           # [H, T, kv_rank]

@@ -18,7 +18,8 @@ ROLE_EMBEDDING = "embedding"  # work dtype; N(0, std)
 ROLE_NORM = "norm"            # float32 vector; 1 (+ N(0, norm_std))
 ROLE_VECTOR = "vector"        # float32 vector or small table (biases, conv taps); N(0, std)
 ROLE_TABLE = "table"          # integer table; int32
-ROLES = (ROLE_MATRIX, ROLE_EMBEDDING, ROLE_NORM, ROLE_VECTOR, ROLE_TABLE)
+ROLE_IDENTITY = "identity"    # small square float32 table around the identity; I (+ N(0, norm_std))
+ROLES = (ROLE_MATRIX, ROLE_EMBEDDING, ROLE_NORM, ROLE_VECTOR, ROLE_TABLE, ROLE_IDENTITY)
 
 
 @dataclass(frozen=True)

@@ -19,7 +19,7 @@ from pathlib import Path
 import torch
 from safetensors import safe_open
 
-from tokenomos_b200.parts.spec import (ROLE_EMBEDDING, ROLE_MATRIX, ROLE_NORM, ROLE_TABLE,
+from tokenomos_b200.parts.spec import (ROLE_EMBEDDING, ROLE_IDENTITY, ROLE_MATRIX, ROLE_NORM, ROLE_TABLE,
                                        ROLE_VECTOR, TensorDecl)
 
 
@@ -103,7 +103,7 @@ def kept_dtype(decl: TensorDecl, stored: torch.dtype, work: torch.dtype) -> torc
     """The dtype a tensor is kept in (see the module docstring)."""
     if decl.role == ROLE_TABLE or not stored.is_floating_point:
         return torch.int32
-    if decl.role in (ROLE_NORM, ROLE_VECTOR):
+    if decl.role in (ROLE_NORM, ROLE_VECTOR, ROLE_IDENTITY):
         return torch.float32
     if decl.role in (ROLE_MATRIX, ROLE_EMBEDDING):
         return work

@@ -16,7 +16,7 @@ from pathlib import Path
 import torch
 from safetensors.torch import save_file
 
-from tokenomos_b200.parts.spec import ROLE_NORM, ROLE_TABLE, TensorDecl
+from tokenomos_b200.parts.spec import ROLE_IDENTITY, ROLE_NORM, ROLE_TABLE, TensorDecl
 
 
 def random_tensors(decls: list[TensorDecl], seed: int, std: float = 0.02, norm_std: float = 0.0,
@@ -36,6 +36,8 @@ def random_tensors(decls: list[TensorDecl], seed: int, std: float = 0.02, norm_s
         t = torch.randn(d.shape, generator=gen, dtype=torch.float32, device=device)
         if d.role == ROLE_NORM:
             t = 1.0 + t * norm_std
+        elif d.role == ROLE_IDENTITY:
+            t = torch.eye(d.shape[0], d.shape[1], dtype=torch.float32, device=device) + t * norm_std
         else:
             t = t * std
         out[d.name] = t.to(dtype)
