@@ -1201,8 +1201,8 @@ def laposun_kernels(z: dict, pk: dict) -> list[dict]:
     nt1 = torch.ones_like(t01)
     dqd, doutd = qd[:B].contiguous(), torch.empty_like(qd[:B])
     add("decode attention over the latent cache, 64 tokens",
-        _timed_us(lambda: ops.attention_latent(dq_lat, dq, cache, dpos, dseq, dtbl, t01, nt1, per, H, D, Dr, win, 0.1),
-                  flush),
+        _timed_us(lambda: ops.attention_latent(dq_lat, dq, cache, dpos, dseq, dtbl, t01, nt1, per, H, D, Dr, win, 0.1,
+                                               nsplit=4), flush),
         _timed_us(lambda: ops.attention_decode_mma(dqd, pool, doutd, dpos, dseq, dtbl, None, win, D ** -0.5, 2,
                                                    gate_e[:B], 4, True, True), flush),
         B * keys * (R + Dr) * 2, B * G * keys * D * 2 * 2, "bytes", "Darizen: decode attention")
@@ -1215,13 +1215,13 @@ def laposun_kernels(z: dict, pk: dict) -> list[dict]:
     down = torch.randn(E, W, ff, device=dev).to(bf) * 0.02
     logits = torch.randn(T, E + 1, device=dev)
     idx, wgt, gate = ops.moe_route(logits, E, top, 1.0, True)
-    tile_rows = ops.gemm_grouped_tile()
+    tile_rows = ops.gemm_grouped_tiles(bf, ff, W, T * top)
     row_token, pair_row, tile_expert = ops.moe_sort(idx, E, tile_rows)
     n_rows = row_token.numel()
 
     def experts():
-        a = ops.gemm_grouped(x, up, tile_expert, row_token, n_rows, act=True)
-        return ops.gemm_grouped(a, down, tile_expert, None, n_rows)
+        a = ops.gemm_grouped(x, up, tile_expert, row_token, n_rows, act=True, tile=tile_rows)
+        return ops.gemm_grouped(a, down, tile_expert, None, n_rows, tile=tile_rows)
 
     wd = torch.randn(top * ff, W, device=dev).to(bf) * 0.02
     wd2 = torch.randn(W, top * ff, device=dev).to(bf) * 0.02

@@ -384,8 +384,21 @@ def test_input_convolution_alone(taps, width):
         entries = [(rid, [0] * (spans[rid][1] - spans[rid][0])) for rid in live]
         ctx, _ = hs.layout(entries)
         h = torch.cat([seqs[rid][slice(*spans[rid])] for rid in live]).cuda()
-        out = ops.canon_conv(h, w_taps.cuda(), hs.cache.states.get((0, "c")), ctx.cu_seqlens, ctx.seq_ctx,
-                             ctx.seq_slot, ctx.tiles(tile), torch.float32)
+        if ctx.host.decode_only:
+            # a step of single tokens: the convolution inside the kernel that reads the streams (one
+            # stream, unit weights, a norm that leaves rows of unit mean square as they are)
+            unit = h / h.pow(2).mean(-1, keepdim=True).sqrt()
+            out = ops.hc_mix_norm(unit.clone(), None, None, None, None, torch.ones(width, device="cuda"), 0.0, 1,
+                                  torch.float32, False,
+                                  conv=(w_taps.cuda(), hs.cache.states.get((0, "c")), ctx.seq_ctx, ctx.seq_slot))
+            # the plain implementation below gets the unit rows too
+            for k, rid in enumerate(live):
+                a, b = spans[rid]
+                seqs[rid] = seqs[rid].clone()
+                seqs[rid][a:b] = unit[k:k + 1].cpu()
+        else:
+            out = ops.canon_conv(h, w_taps.cuda(), hs.cache.states.get((0, "c")), ctx.cu_seqlens, ctx.seq_ctx,
+                                 ctx.seq_slot, ctx.tiles(tile), torch.float32)
         hs.commit(entries)
         o = 0
         for rid, toks in entries:
@@ -440,8 +453,9 @@ class LatentSequence:
         q_lat = q[a:b, :, :self.R].transpose(0, 1).to(self.dtype).cuda().contiguous()       # D >= R in these tests
         per_tile = ops.attention_latent_tokens(self.H, self.D, self.R, self.Dr, self.dtype)
         _, tok0, _, ntok = ctx.tiles(per_tile)
+        # (a single token's keys shared out over three CTAs where the tensor-core form runs)
         out = ops.attention_latent(q_lat, qq, cache, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
-                                   self.H, self.D, self.Dr, window, scale)
+                                   self.H, self.D, self.Dr, window, scale, nsplit=3 if b - a == 1 else 1)
         self.hs.commit([("x", [0] * (b - a))])
         return out.transpose(0, 1).double().cpu()
 
@@ -525,9 +539,16 @@ def test_batched_and_grouped_products():
         want = torch.einsum("gmk,gnk->gmn", a16.double(), w16.double())
         got = ops.gemm_batched(a16, w16).double()
         assert (got - want).abs().max() < 1e-2 * want.abs().max()
+    # the same writing [M, G, N] through a view, every row times the sigmoid of its gate
+    a16 = torch.randn(3, 70, 72, generator=g).to(torch.bfloat16).cuda()
+    w16 = torch.randn(3, 40, 72, generator=g).to(torch.bfloat16).cuda()
+    gate = torch.randn(70, 11, generator=g).to(torch.bfloat16).cuda()[:, 4:7]
+    out = torch.empty(70, 3, 40, dtype=torch.bfloat16, device="cuda")
+    ops.gemm_batched(a16, w16, out=out.transpose(0, 1), gate=gate)
+    want = torch.einsum("gmk,gnk->mgn", a16.double(), w16.double()) * torch.sigmoid(gate.double())[:, :, None]
+    assert (out.double() - want).abs().max() < 1e-2 * want.abs().max()
     # grouped, with gathered rows, zero rows and unused tiles
-    tile = ops.gemm_grouped_tile()
-    for dtype in (torch.float32, torch.bfloat16):
+    for dtype, tile in ((torch.float32, 64), (torch.bfloat16, 64), (torch.bfloat16, 128)):
         x = torch.randn(50, 64, generator=g).to(torch.bfloat16).to(dtype).cuda()
         w3 = torch.randn(3, 72, 64, generator=g).to(torch.bfloat16).to(dtype).cuda()
         rows = 4 * tile
@@ -536,7 +557,7 @@ def test_batched_and_grouped_products():
         row_index[tile:tile + 2] = torch.tensor([1, 2])
         row_index[3 * tile:3 * tile + tile] = torch.arange(tile) % 50
         groups = torch.tensor([2, 0, -1, 1], dtype=torch.int32)
-        got = ops.gemm_grouped(x, w3, groups.cuda(), row_index.cuda(), rows, act=True).double().cpu()
+        got = ops.gemm_grouped(x, w3, groups.cuda(), row_index.cuda(), rows, act=True, tile=tile).double().cpu()
         for t, grp in enumerate(groups.tolist()):
             if grp < 0:
                 continue

@@ -112,7 +112,8 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 hc_mix_norm_kernel(float* streams, const T* y, int64_t y_stride, const float* __restrict__ mix,
                    const float* __restrict__ out_w, const float* __restrict__ in_w,
-                   const float* __restrict__ norm_w, float eps, float* h32, T* h16, int S, int width) {
+                   const float* __restrict__ norm_w, float eps, float* h32, T* h16, int S, int width,
+                   const float* __restrict__ taps, float* state, const int* seq_ctx, const int* seq_slot, int K) {
     pdl_launch_dependents();
     extern __shared__ float u_s[];
     __shared__ float red[33];
@@ -127,6 +128,18 @@ hc_mix_norm_kernel(float* streams, const T* y, int64_t y_stride, const float* __
     const size_t t = blockIdx.x;
     float* xs = streams + t * S * width;
     float ss = 0.f;
+    // a step of single tokens with the input convolution inside: the state's rows are asked for
+    // first, so that they travel while the streams are summed
+    float* old_s = u_s + width;                 // [K - 1][width]
+    float* st = nullptr;
+    if (taps != nullptr && K > 1) {
+        const int ctx = seq_ctx[t];
+        st = state + (size_t)TK_SLOT(TK_K_HYPER, seq_slot[t]) * (K - 1) * width;
+        for (int r = 0; r < K - 1; ++r) {
+            const bool live = ctx - (K - 1) + r >= 0;      // rows of positions before the sequence's start read as zeros
+            for (int i = threadIdx.x; i < width; i += blockDim.x) old_s[r * width + i] = live ? st[(size_t)r * width + i] : 0.f;
+        }
+    }
     if constexpr (VEC) {
         for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
             float4 x[MAX_STREAMS];
@@ -200,6 +213,20 @@ hc_mix_norm_kernel(float* streams, const T* y, int64_t y_stride, const float* __
     }
     if (norm_w == nullptr) return;
     const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+    if (taps != nullptr) {
+        // row t is sequence t's only token; rows of the state: positions ctx - (K - 1) .. ctx - 1
+        // (each thread reads and writes the same channels of old_s that it filled above)
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = u_s[i] * rstd * norm_w[i];
+            const float* w = taps + (size_t)i * K;
+            float acc = v + w[K - 1] * v;
+            for (int r = 0; r < K - 1; ++r) acc = fmaf(w[r], old_s[r * width + i], acc);
+            h16[t * width + i] = from_f<T>(acc);
+            for (int r = 0; r < K - 2; ++r) st[(size_t)r * width + i] = old_s[(r + 1) * width + i];
+            if (K > 1) st[(size_t)(K - 2) * width + i] = v;
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
         const float v = u_s[i] * rstd * norm_w[i];
         if (h32 != nullptr) h32[t * width + i] = v;
@@ -210,20 +237,26 @@ hc_mix_norm_kernel(float* streams, const T* y, int64_t y_stride, const float* __
 TK_API int tk_hc_mix_norm(float* streams, const void* y, int64_t y_stride, const float* mix,
                           const float* out_w, const float* in_w, const float* norm_w, float eps,
                           float* h32, void* h16, int tokens, int S, int width, int dtype,
+                          const float* taps, float* state, const int* seq_ctx, const int* seq_slot, int K,
                           cudaStream_t stream) {
     TK_CHECK_ARG(tokens >= 0 && width > 0, "hc_mix_norm: bad sizes");
+    TK_CHECK_ARG(taps == nullptr || (K >= 1 && K <= MAX_TAPS && h16 != nullptr && norm_w != nullptr && seq_ctx != nullptr &&
+                                     seq_slot != nullptr && (K == 1 || state != nullptr)),
+                 "hc_mix_norm: the input convolution of a step of single tokens needs 1..%d taps, a state and an output", MAX_TAPS);
     TK_CHECK_ARG(S >= 1 && S <= MAX_STREAMS, "hc_mix_norm: %d streams; 1..%d are built", S, MAX_STREAMS);
     TK_CHECK_ARG((size_t)width * 4 <= 200 * 1024, "hc_mix_norm: a width of %d does not fit shared memory", width);
     TK_CHECK_ARG(norm_w == nullptr || h32 != nullptr || h16 != nullptr, "hc_mix_norm: a norm needs an output");
     if (tokens == 0) return 0;
-    const size_t smem = (size_t)width * sizeof(float);
+    const size_t smem = (size_t)width * sizeof(float) * (taps != nullptr ? K : 1);
+    TK_CHECK_ARG(smem <= 200 * 1024, "hc_mix_norm: %d taps of width %d do not fit shared memory", K, width);
     const bool vec = width % 4 == 0 && (y == nullptr || (y_stride % 4 == 0 && ((uintptr_t)y % 16) == 0)) &&
                      ((uintptr_t)streams % 16) == 0;
 #define TK_HC(TT, V)                                                                                          \
     do {                                                                                                      \
         cudaFuncSetAttribute(hc_mix_norm_kernel<TT, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         tk_launch(hc_mix_norm_kernel<TT, V>, dim3(tokens), dim3(256), smem, stream, streams, (const TT*)y,     \
-                  y_stride, mix, out_w, in_w, norm_w, eps, h32, (TT*)h16, S, width);                           \
+                  y_stride, mix, out_w, in_w, norm_w, eps, h32, (TT*)h16, S, width, taps, state, seq_ctx,      \
+                  seq_slot, K);                                                                                \
     } while (0)
     if (dtype == TK_F32) { if (vec) TK_HC(float, true); else TK_HC(float, false); }
     else if (dtype == TK_BF16) { if (vec) TK_HC(__nv_bfloat16, true); else TK_HC(__nv_bfloat16, false); }

@@ -384,7 +384,8 @@ __global__ void __launch_bounds__(A_THREADS, 1)
 attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                        __nv_bfloat16* out, const int* positions, const int* tok_seq, const int* block_table,
                        int bt_stride, const int* tile_tok0, const int* tile_ntok, int tokens, int H, int D, int R,
-                       int Dr, int P, int window, float scale, int heads_per_chunk) {
+                       int Dr, int P, int window, float scale, int heads_per_chunk, int nsplit, float* part_o,
+                       float* part_ml) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -425,7 +426,11 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
     const int pos_first = row_pos[0];
     const int pos_last = row_pos[rows - 1];
     const int lo = window > 0 ? max(0, pos_first - window + 1) : 0;
-    const int n_it = (pos_last - lo) / AN + 1;
+    const int n_all = (pos_last - lo) / AN + 1;
+    // this CTA's share of the key tiles (blockIdx.z of nsplit; an empty share leaves zeros)
+    const int per_split = (n_all + nsplit - 1) / nsplit;
+    const int it_begin = blockIdx.z * per_split;
+    const int n_it = min(n_all, it_begin + per_split);
 
     auto load_keys = [&](int it, int stage) {
         const int key = tid >> 2;
@@ -439,7 +444,7 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
         __nv_bfloat16* dst = Ks + ((size_t)stage * AN + key) * KLD;
         for (int ch = tid & 3; ch < chunks; ch += 4) a_cp_async16(dst + ch * 8, src + ch * 8, valid);
     };
-    load_keys(0, 0);
+    if (it_begin < n_it) load_keys(it_begin, 0);
     asm volatile("cp.async.commit_group;" ::: "memory");
 
     const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;
@@ -451,12 +456,12 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
     const int nb = R / 32;                  // n8 blocks of my column quarter
     const int col0 = wq * (R / 4);
 
-    for (int it = 0; it < n_it; ++it) {
+    for (int it = it_begin; it < n_it; ++it) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        if (it + 1 < n_it) load_keys(it + 1, (it + 1) & 1);
+        if (it + 1 < n_it) load_keys(it + 1, (it + 1 - it_begin) & 1);
         asm volatile("cp.async.commit_group;" ::: "memory");
-        const __nv_bfloat16* ks = Ks + (size_t)(it & 1) * AN * KLD;
+        const __nv_bfloat16* ks = Ks + (size_t)((it - it_begin) & 1) * AN * KLD;
         // ---- scores of my 16 rows against my 16 keys ----
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         {
@@ -557,6 +562,28 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
         t0 += red_sum[(rg * 4 + w) * 16 + (lane >> 2)];
         t1 += red_sum[(rg * 4 + w) * 16 + (lane >> 2) + 8];
     }
+    if (nsplit > 1) {
+        // my share, not normalised, with its maximum and sum: the merge kernel finishes the rows
+        const size_t base = (size_t)blockIdx.z * H * tokens;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = half ? r1 : r0;
+            if (r >= rows) continue;
+            const int t = tok0 + r / gh, h = g0 + r % gh;
+            const size_t row = base + (size_t)h * tokens + t;
+            if (wq == 0 && (lane & 3) == 0) {
+                part_ml[row * 2] = half ? m1 : m0;
+                part_ml[row * 2 + 1] = half ? t1 : t0;
+            }
+#pragma unroll
+            for (int j = 0; j < MAXNB; ++j) {
+                if (j >= nb) break;
+                const int col = col0 + j * 8 + (lane & 3) * 2;
+                *reinterpret_cast<float2*>(part_o + row * R + col) = make_float2(acc[j][half * 2], acc[j][half * 2 + 1]);
+            }
+        }
+        return;
+    }
     const float inv0 = t0 > 0.f ? 1.0f / t0 : 0.f, inv1 = t1 > 0.f ? 1.0f / t1 : 0.f;
 #pragma unroll
     for (int j = 0; j < MAXNB; ++j) {
@@ -585,7 +612,10 @@ TK_API int tk_attn_latent_mma_supported(int D, int R, int Dr) {
 TK_API int tk_attn_latent_mma(const void* q_lat, const void* q, const void* cache, void* out, const int* positions,
                               const int* tok_seq, const int* block_table, int bt_stride, const int* tile_tok0,
                               const int* tile_ntok, int n_tiles, int tokens_per_tile, int tokens, int H, int D, int R,
-                              int Dr, int P, int window, float scale, cudaStream_t stream) {
+                              int Dr, int P, int window, float scale, int nsplit, float* part_o, float* part_ml,
+                              cudaStream_t stream) {
+    TK_CHECK_ARG(nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || (part_o != nullptr && part_ml != nullptr)),
+                 "latent attention (mma): %d shares of the keys need scratch memory", nsplit);
     TK_CHECK_ARG(tk_attn_latent_mma_supported(D, R, Dr), "latent attention (mma): sizes D=%d R=%d Dr=%d", D, R, Dr);
     TK_CHECK_ARG(H > 0 && P > 0 && n_tiles >= 0 && tokens >= 0, "latent attention (mma): bad counts");
     TK_CHECK_ARG(tokens_per_tile >= 1 && tokens_per_tile <= AM, "latent attention (mma): %d tokens per tile", tokens_per_tile);
@@ -593,13 +623,14 @@ TK_API int tk_attn_latent_mma(const void* q_lat, const void* q, const void* cach
     const int hpc = min(H, AM / tokens_per_tile);
     const int KLD = R + Dr + 8;
     const size_t smem = (size_t)(AM + 2 * AN) * KLD * 2 + (size_t)AM * PLD * 2 + 256 * sizeof(float);
-    dim3 grid(n_tiles, (H + hpc - 1) / hpc);
+    dim3 grid(n_tiles, (H + hpc - 1) / hpc, nsplit);
 #define TK_ALM(NB)                                                                                                 \
     do {                                                                                                           \
         cudaFuncSetAttribute(attn_latent_mma_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
         tk_launch(attn_latent_mma_kernel<NB>, grid, dim3(A_THREADS), smem, stream, (const __nv_bfloat16*)q_lat,     \
                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, positions, tok_seq,   \
-                  block_table, bt_stride, tile_tok0, tile_ntok, tokens, H, D, R, Dr, P, window, scale, hpc);       \
+                  block_table, bt_stride, tile_tok0, tile_ntok, tokens, H, D, R, Dr, P, window, scale, hpc, nsplit, \
+                  part_o, part_ml);                                                                                \
     } while (0)
     const int nb = R / 32;
     if (nb <= 2) TK_ALM(2);
@@ -608,5 +639,56 @@ TK_API int tk_attn_latent_mma(const void* q_lat, const void* q, const void* cach
     else TK_ALM(16);
 #undef TK_ALM
     TK_CHECK_LAUNCH("attn_latent_mma");
+    return 0;
+}
+
+// out[h, t, :] = sum_s w_s O_s / sum_s w_s l_s with w_s = exp(m_s - max m): the shares of a row's keys
+// that several CTAs took, merged. One block per row (h, t).
+__global__ void __launch_bounds__(128)
+attn_latent_merge_kernel(const float* part_o, const float* part_ml, __nv_bfloat16* out, int rows, int R, int nsplit) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float w_s[64];
+    __shared__ float inv_s;
+    const size_t row = blockIdx.x;
+    if (threadIdx.x < 32) {
+        // the shares' maxima and sums in one trip: lane s takes shares s and s + 32
+        float m[2], l[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const int s = threadIdx.x + 32 * k;
+            m[k] = s < nsplit ? part_ml[((size_t)s * rows + row) * 2] : -INFINITY;
+            l[k] = s < nsplit ? part_ml[((size_t)s * rows + row) * 2 + 1] : 0.f;
+        }
+        const float mx = warp_max(fmaxf(m[0], m[1]));
+        float total = 0.f;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float w = (m[k] == -INFINITY) ? 0.f : expf(m[k] - mx);
+            w_s[threadIdx.x + 32 * k] = w;
+            total += w * l[k];
+        }
+        total = warp_sum(total);
+        if (threadIdx.x == 0) inv_s = total > 0.f ? 1.0f / total : 0.f;
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float v = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            const float w = w_s[s];
+            if (w != 0.f) v = fmaf(w, part_o[((size_t)s * rows + row) * R + c], v);
+        }
+        out[row * R + c] = __float2bfloat16_rn(v * inv);
+    }
+}
+
+TK_API int tk_attn_latent_merge(const float* part_o, const float* part_ml, void* out, int rows, int R, int nsplit,
+                                cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && R > 0 && nsplit >= 1, "latent attention merge: bad sizes");
+    if (rows == 0) return 0;
+    tk_launch(attn_latent_merge_kernel, dim3(rows), dim3(128), 0, stream, part_o, part_ml, (__nv_bfloat16*)out, rows, R,
+              nsplit);
+    TK_CHECK_LAUNCH("attn_latent_merge");
     return 0;
 }

@@ -312,7 +312,7 @@ TK_API int tk_relu2(void* x, int64_t n, int dtype, cudaStream_t stream) {
 // in whole 16-byte chunks and 16-byte aligned rows.
 // ---------------------------------------------------------------------------------------------
 namespace {
-constexpr int GM = 64, GN = 128, GK = 32, GLD = 40, GSTAGES = 3, G_THREADS = 256;
+constexpr int GN = 128, GK = 32, GLD = 40, G_THREADS = 256;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -335,15 +335,21 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 }
 }  // namespace
 
+// GM: rows of a tile (64: 8 warps of 32 x 32; 128: 8 warps of 64 x 32); GSTAGES: copies in flight.
+// gate (batched form only): C[g][m][:] *= sigmoid(gate[m * gate_stride + g]).
+template <int GM, int GSTAGES>
 __global__ void __launch_bounds__(G_THREADS)
 gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const int* row_index,
                         const __nv_bfloat16* __restrict__ W, int64_t ldw, int64_t w_gs, const int* tile_group,
-                        __nv_bfloat16* C, int64_t ldc, int64_t c_gs, int M, int N, int K, int act) {
+                        __nv_bfloat16* C, int64_t ldc, int64_t c_gs, int M, int N, int K, int act,
+                        const __nv_bfloat16* gate, int64_t gate_stride) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ __align__(16) __nv_bfloat16 As[GSTAGES][GM * GLD];
-    __shared__ __align__(16) __nv_bfloat16 Ws[GSTAGES][GN * GLD];
+    extern __shared__ __align__(16) unsigned char gsm[];
+    __nv_bfloat16 (*As)[GM * GLD] = reinterpret_cast<__nv_bfloat16 (*)[GM * GLD]>(gsm);
+    __nv_bfloat16 (*Ws)[GN * GLD] = reinterpret_cast<__nv_bfloat16 (*)[GN * GLD]>(gsm + (size_t)GSTAGES * GM * GLD * 2);
     __shared__ int rows_s[GM];
+    constexpr int MI = GM / 32;              // m16 blocks of a warp's tile
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
     if (tile_group != nullptr) {
@@ -360,13 +366,20 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
         rows_s[tid] = m < M ? (row_index != nullptr ? row_index[m] : m) : -1;
     }
     __syncthreads();
-    const int a_row = tid >> 2, a_chunk = (tid & 3) * 8;          // one 16-byte chunk of the A tile per thread
-    const int a_src = rows_s[a_row];
+    const int a_chunk = (tid & 3) * 8;          // 16-byte chunks: 4 a row, rows 64 apart per thread
+    int a_src[GM / 64];
+#pragma unroll
+    for (int i = 0; i < GM / 64; ++i) a_src[i] = rows_s[(tid >> 2) + i * 64];
+    const int gz = tile_group != nullptr ? 0 : blockIdx.z;
     const int ktiles = (K + GK - 1) / GK;
     auto load = [&](int kt, int stage) {
         const int k = kt * GK + a_chunk;
-        const bool av = a_src >= 0 && k < K;
-        cp_async16(&As[stage][a_row * GLD + a_chunk], av ? (const void*)(A + (size_t)a_src * lda + k) : (const void*)A, av);
+#pragma unroll
+        for (int i = 0; i < GM / 64; ++i) {
+            const bool av = a_src[i] >= 0 && k < K;
+            cp_async16(&As[stage][((tid >> 2) + i * 64) * GLD + a_chunk],
+                       av ? (const void*)(A + (size_t)a_src[i] * lda + k) : (const void*)A, av);
+        }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int r = (tid >> 2) + i * 64;
@@ -379,10 +392,10 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
         if (s < ktiles) load(s, s);
         cp_async_commit();
     }
-    const int wm = (warp >> 2) * 32, wn = (warp & 3) * 32;
-    float acc[2][4][4];
+    const int wm = (warp >> 2) * (GM / 2), wn = (warp & 3) * 32;
+    float acc[MI][4][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < MI; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -396,26 +409,27 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
         const __nv_bfloat16* ws = Ws[kt % GSTAGES];
 #pragma unroll
         for (int kk = 0; kk < GK; kk += 16) {
-            unsigned a[2][4], b[2][4];
+            unsigned a[MI][4], b[2][4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < MI; ++i)
                 ldmatrix_x4(a[i], as + (wm + i * 16 + (lane & 15)) * GLD + kk + (lane >> 4) * 8);
 #pragma unroll
             for (int j = 0; j < 2; ++j)
                 ldmatrix_x4(b[j], ws + (wn + j * 16 + (lane & 7) + (lane >> 4) * 8) * GLD + kk + ((lane >> 3) & 1) * 8);
 #pragma unroll
-            for (int i = 0; i < 2; ++i)
+            for (int i = 0; i < MI; ++i)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
         }
     }
     cp_async_wait<0>();
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < MI; ++i) {
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             const int m = m0 + wm + i * 16 + (lane >> 2) + half * 8;
             if (m >= M) continue;
+            const float gv = gate != nullptr ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)m * gate_stride + gz]))) : 1.0f;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int n = n0 + wn + j * 8 + (lane & 3) * 2;
@@ -425,7 +439,7 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
                     v0 = fmaxf(v0, 0.f); v0 *= v0;
                     v1 = fmaxf(v1, 0.f); v1 *= v1;
                 }
-                *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + n) = __floats2bfloat162_rn(v0, v1);
+                *reinterpret_cast<__nv_bfloat162*>(C + (size_t)m * ldc + n) = __floats2bfloat162_rn(v0 * gv, v1 * gv);
             }
         }
     }
@@ -433,8 +447,11 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
 
 TK_API int tk_gemm_grouped_mma(const void* A, int64_t lda, int64_t a_gs, const int* row_index, const void* W,
                                int64_t ldw, int64_t w_gs, const int* tile_group, void* C, int64_t ldc,
-                               int64_t c_gs, int M, int N, int K, int groups, int act, cudaStream_t stream) {
+                               int64_t c_gs, int M, int N, int K, int groups, int act, int tile_rows,
+                               const void* gate, int64_t gate_stride, cudaStream_t stream) {
     TK_CHECK_ARG(M >= 0 && N > 0 && K > 0 && groups >= 1, "gemm_grouped_mma: bad sizes M=%d N=%d K=%d", M, N, K);
+    TK_CHECK_ARG(tile_rows == 64 || tile_rows == 128, "gemm_grouped_mma: tiles of %d rows; 64 or 128", tile_rows);
+    TK_CHECK_ARG(gate == nullptr || tile_group == nullptr, "gemm_grouped_mma: the row gate belongs to the batched form");
     TK_CHECK_ARG(K % 8 == 0 && N % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && ldc % 2 == 0 && a_gs % 8 == 0 &&
                      w_gs % 8 == 0 && c_gs % 2 == 0,
                  "gemm_grouped_mma: K, N and the strides must be whole 16-byte chunks");
@@ -442,9 +459,18 @@ TK_API int tk_gemm_grouped_mma(const void* A, int64_t lda, int64_t a_gs, const i
                  "gemm_grouped_mma: operands must be 16-byte aligned");
     TK_CHECK_ARG(act == 0 || act == 1, "gemm_grouped_mma: activation %d", act);
     if (M == 0) return 0;
-    dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM, tile_group != nullptr ? 1 : groups);
-    tk_launch(gemm_grouped_mma_kernel, grid, dim3(G_THREADS), 0, stream, (const __nv_bfloat16*)A, lda, a_gs, row_index,
-              (const __nv_bfloat16*)W, ldw, w_gs, tile_group, (__nv_bfloat16*)C, ldc, c_gs, M, N, K, act);
+    dim3 grid((N + GN - 1) / GN, (M + tile_rows - 1) / tile_rows, tile_group != nullptr ? 1 : groups);
+#define TK_GG(GMV, ST)                                                                                              \
+    do {                                                                                                            \
+        const size_t smem = (size_t)ST * (GMV + GN) * GLD * 2;                                                      \
+        cudaFuncSetAttribute(gemm_grouped_mma_kernel<GMV, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        tk_launch(gemm_grouped_mma_kernel<GMV, ST>, grid, dim3(G_THREADS), smem, stream, (const __nv_bfloat16*)A, lda, \
+                  a_gs, row_index, (const __nv_bfloat16*)W, ldw, w_gs, tile_group, (__nv_bfloat16*)C, ldc, c_gs, M, N, \
+                  K, act, (const __nv_bfloat16*)gate, gate_stride);                                                 \
+    } while (0)
+    if (tile_rows == 64) TK_GG(64, 5);
+    else TK_GG(128, 4);
+#undef TK_GG
     TK_CHECK_LAUNCH("gemm_grouped_mma");
     return 0;
 }

@@ -829,12 +829,20 @@ def embed_bigram_norm(table: torch.Tensor, bigram: torch.Tensor | None, norm_w: 
 
 def hc_mix_norm(streams: torch.Tensor, y: torch.Tensor | None, mix: torch.Tensor | None, out_w: torch.Tensor | None,
                 in_w: torch.Tensor | None, norm_w: torch.Tensor | None, eps: float, n_streams: int,
-                out_dtype: torch.dtype, keep32: bool) -> torch.Tensor | None:
+                out_dtype: torch.dtype, keep32: bool, conv: tuple | None = None) -> torch.Tensor | None:
     """Streams ``[T, S * width]`` float32, in place: ``x'_t = sum_s mix[s, t] x_s + out_w[t] * y``
     (when ``y`` [T, width] is given; ``mix`` None: identity, ``out_w`` None: ones), then
     ``h = rmsnorm(sum_s in_w[s] x'_s) * norm_w`` (``in_w`` None: ones): float32 when ``keep32``, else
-    ``out_dtype``. ``norm_w`` None: only the write, returns None."""
+    ``out_dtype``. ``norm_w`` None: only the write, returns None. ``conv``: ``(taps, state, seq_ctx,
+    seq_slot)`` in a step where every sequence brings one token: the input convolution
+    (``canon_conv``) and its state update in the same kernel; the result is in ``out_dtype``."""
     _cuda(streams, y, mix, out_w, in_w, norm_w)
+    taps, state, seq_ctx, seq_slot = conv if conv is not None else (None, None, None, None)
+    if conv is not None:
+        keep32 = False
+        if taps.dtype != torch.float32 or not taps.is_contiguous() or (
+                state is not None and (state.dtype != torch.float32 or not state.is_contiguous())):
+            raise KernelError("hc_mix_norm: taps and state are contiguous float32 tensors")
     S = int(n_streams)
     T, width = streams.shape[0], streams.shape[1] // S
     if streams.dtype != torch.float32 or not streams.is_contiguous() or streams.shape[1] != S * width:
@@ -848,7 +856,8 @@ def hc_mix_norm(streams: torch.Tensor, y: torch.Tensor | None, mix: torch.Tensor
     _lib.call("tk_hc_mix_norm", _ptr(streams), _ptr(y), y.stride(0) if y is not None else 0,
               _ptr(_f32vec(mix, "mix", S * S)), _ptr(_f32vec(out_w, "out", S)), _ptr(_f32vec(in_w, "in", S)),
               _ptr(_f32vec(norm_w, "norm weight", width)), float(eps), _ptr(h if keep32 else None),
-              _ptr(None if keep32 else h), T, S, width, code, _stream())
+              _ptr(None if keep32 else h), T, S, width, code, _ptr(taps), _ptr(state), _ptr(seq_ctx), _ptr(seq_slot),
+              taps.shape[1] if taps is not None else 0, _stream())
     return h
 
 
@@ -934,9 +943,11 @@ ATTENTION_LATENT_MAX_RANK = 512
 def attention_latent(q_lat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
                      tok_seq: torch.Tensor, block_table: torch.Tensor, tile_tok0: torch.Tensor,
                      tile_ntok: torch.Tensor, tokens_per_tile: int, heads: int, dim: int, rot_dim: int,
-                     window: int | None, scale: float) -> torch.Tensor:
+                     window: int | None, scale: float, nsplit: int = 1) -> torch.Tensor:
     """Windowed causal attention over the latent cache [pages, P, R + rot_dim]: scores
-    ``(q_lat[h, t] . c_j + q[t, h, dim:] . k_rot_j) * scale``, output ``sum_j p_j c_j`` as [heads, T, R]."""
+    ``(q_lat[h, t] . c_j + q[t, h, dim:] . k_rot_j) * scale``, output ``sum_j p_j c_j`` as [heads, T, R].
+    ``nsplit`` > 1 (tensor-core form only): that many CTAs share a tile's keys and a second kernel
+    merges their shares, for steps with few tiles behind long contexts."""
     _cuda(q_lat, q, cache, positions, tok_seq, block_table, tile_tok0, tile_ntok)
     H, T, R = q_lat.shape
     if (H != heads or not q_lat.is_contiguous() or not q.is_contiguous() or q.shape[0] != T
@@ -948,7 +959,10 @@ def attention_latent(q_lat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, 
         _lib.call("tk_attn_latent_mma", _ptr(q_lat), _ptr(q), _ptr(cache), _ptr(out), _ptr(_i32(positions, "positions")),
                   _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
                   _ptr(_i32(tile_tok0, "tile_tok0")), _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(),
-                  int(tokens_per_tile), T, H, dim, R, rot_dim, cache.shape[1], int(window or 0), float(scale), _stream())
+                  int(tokens_per_tile), T, H, dim, R, rot_dim, cache.shape[1], int(window or 0), float(scale), 1, None,
+                  None, _stream()) if nsplit <= 1 else _attention_latent_split(
+                      q_lat, q, cache, out, positions, tok_seq, block_table, tile_tok0, tile_ntok, tokens_per_tile, dim,
+                      rot_dim, window, scale, int(nsplit))
         return out
     _lib.call("tk_attn_latent", _ptr(q_lat), _ptr(q), _ptr(cache), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
@@ -956,6 +970,18 @@ def attention_latent(q_lat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, 
               int(tokens_per_tile), T, H, dim, R, rot_dim, cache.shape[1], int(window or 0), float(scale),
               _dtype_code(q), _stream())
     return out
+
+
+def _attention_latent_split(q_lat, q, cache, out, positions, tok_seq, block_table, tile_tok0, tile_ntok,
+                            tokens_per_tile, dim, rot_dim, window, scale, nsplit) -> None:
+    H, T, R = q_lat.shape
+    part_o = torch.empty(nsplit, H, T, R, dtype=torch.float32, device=q.device)
+    part_ml = torch.empty(nsplit, H, T, 2, dtype=torch.float32, device=q.device)
+    _lib.call("tk_attn_latent_mma", _ptr(q_lat), _ptr(q), _ptr(cache), _ptr(out), _ptr(positions), _ptr(tok_seq),
+              _ptr(block_table), block_table.stride(0), _ptr(tile_tok0), _ptr(tile_ntok), tile_tok0.numel(),
+              int(tokens_per_tile), T, H, dim, R, rot_dim, cache.shape[1], int(window or 0), float(scale), nsplit,
+              _ptr(part_o), _ptr(part_ml), _stream())
+    _lib.call("tk_attn_latent_merge", _ptr(part_o), _ptr(part_ml), _ptr(out), H * T, R, nsplit, _stream())
 
 
 def head_gate_transpose(x: torch.Tensor, gate: torch.Tensor | None) -> torch.Tensor:
@@ -1010,8 +1036,15 @@ def moe_sort(idx: torch.Tensor, experts: int, tile: int):
     return row_token, pair_row, tile_expert
 
 
+def gemm_grouped_tiles(a_dtype: torch.dtype, n: int, k: int, rows: int) -> int:
+    """Rows of a tile of the grouped product, which the sort of the rows has to use too: 64, or, in
+    the tensor-core form when there are many rows, 128."""
+    big = a_dtype == torch.bfloat16 and k % 8 == 0 and n % 8 == 0 and rows >= 2048
+    return 128 if big else _lib.call("tk_gemm_grouped_tile")
+
+
 def gemm_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row_index: torch.Tensor | None,
-                 rows: int, act: bool = False) -> torch.Tensor:
+                 rows: int, act: bool = False, tile: int = 64) -> torch.Tensor:
     """``out[m] = act(a[row_index[m]] @ w[g].T)`` with ``g = tile_group[m // tile]``; ``w`` [G, N, K];
     a row index of -1 reads zeros, a tile group of -1 is skipped (its rows are not written)."""
     _cuda(a, w, tile_group, row_index)
@@ -1021,8 +1054,11 @@ def gemm_grouped(a: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, row
     out = torch.empty(rows, N, dtype=a.dtype, device=a.device)
     if _grouped_mma_ok(a, w, N, K):
         _lib.call("tk_gemm_grouped_mma", _ptr(a), a.stride(0), 0, _ptr(row_index), _ptr(w), K, N * K,
-                  _ptr(_i32(tile_group, "tile_group")), _ptr(out), N, 0, rows, N, K, G, int(bool(act)), _stream())
+                  _ptr(_i32(tile_group, "tile_group")), _ptr(out), N, 0, rows, N, K, G, int(bool(act)), int(tile),
+                  None, 0, _stream())
         return out
+    if tile != _lib.call("tk_gemm_grouped_tile"):
+        raise KernelError(f"gemm_grouped: tiles of {tile} rows are the tensor-core form's")
     _lib.call("tk_gemm_grouped_simt", _ptr(a), a.stride(0), 0, _ptr(row_index), _ptr(w), K, N * K,
               _ptr(_i32(tile_group, "tile_group")), _ptr(out), N, 0, rows, N, K, G, int(bool(act)), _dtype_code(a),
               _stream())
@@ -1036,10 +1072,13 @@ def _grouped_mma_ok(a: torch.Tensor, w: torch.Tensor, N: int, K: int) -> bool:
             and w.stride(-2) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``out[g] = a[g] @ w[g].T`` on the CUDA cores (32-bit FMA): ``a`` [G, M, K] (any strides with
-    contiguous columns), ``w`` [G, N, K] likewise, ``out`` [G, M, N]."""
-    _cuda(a, w, out)
+def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+                 gate: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[g] = a[g] @ w[g].T``: ``a`` [G, M, K] (any strides with contiguous columns), ``w``
+    [G, N, K] likewise, ``out`` [G, M, N] (any strides too: a view of [M, G, N] works). 32-bit FMA on
+    the CUDA cores, or mma.sync for bfloat16 in whole 16-byte chunks. ``gate`` [M, G] (tensor-core
+    form only): row m of ``out[g]`` times ``sigmoid(gate[m, g])``."""
+    _cuda(a, w, out, gate)
     G, M, K = a.shape
     N = w.shape[1]
     if a.dtype != w.dtype or a.stride(2) != 1 or w.stride(2) != 1 or w.shape[0] != G or w.shape[2] != K:
@@ -1050,9 +1089,14 @@ def gemm_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = No
         raise KernelError("gemm_batched: out needs contiguous columns")
     if (_grouped_mma_ok(a, w, N, K) and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and out.stride(1) % 2 == 0
             and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0):
+        if gate is not None and (gate.dtype != torch.bfloat16 or gate.stride(1) != 1 or tuple(gate.shape) != (M, G)):
+            raise KernelError("gemm_batched: the gate is bfloat16 [M, G] with contiguous columns")
         _lib.call("tk_gemm_grouped_mma", _ptr(a), a.stride(1), a.stride(0), None, _ptr(w), w.stride(1), w.stride(0),
-                  None, _ptr(out), out.stride(1), out.stride(0), M, N, K, G, 0, _stream())
+                  None, _ptr(out), out.stride(1), out.stride(0), M, N, K, G, 0, 64 if M <= 64 else 128, _ptr(gate),
+                  gate.stride(0) if gate is not None else 0, _stream())
         return out
+    if gate is not None:
+        raise KernelError("gemm_batched: the row gate needs the tensor-core form (bfloat16, 16-byte chunks)")
     _lib.call("tk_gemm_grouped_simt", _ptr(a), a.stride(1), a.stride(0), None, _ptr(w), w.stride(1), w.stride(0),
               None, _ptr(out), out.stride(1), out.stride(0), M, N, K, G, 0, _dtype_code(a), _stream())
     return out

@@ -69,7 +69,7 @@ _SIGNATURES = {
     "tk_sample_status": [],
     "tk_gemm_tc_decode": [P, L, P, L, P, P, L, I, I, I, I, I, I, P],
     "tk_embed_bigram_norm": [P, P, P, F, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
-    "tk_hc_mix_norm": [P, P, L, P, P, P, P, F, P, P, I, I, I, I, P],
+    "tk_hc_mix_norm": [P, P, L, P, P, P, P, F, P, P, I, I, I, I, P, P, P, P, I, P],
     "tk_canon_conv": [P, P, P, P, P, P, P, P, P, P, I, P, I, I, I, P],
     "tk_latent_prepare": [P, L, P, P, F, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P],
     "tk_latent_rotate_q": [P, P, P, I, I, I, I, I, I, P],
@@ -78,13 +78,14 @@ _SIGNATURES = {
     "tk_attn_latent": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
     "tk_attn_latent_mma_rows": [],
     "tk_attn_latent_mma_supported": [I, I, I],
-    "tk_attn_latent_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, P],
+    "tk_attn_latent_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P, P],
+    "tk_attn_latent_merge": [P, P, P, I, I, I, P],
     "tk_head_gate_transpose": [P, P, L, P, I, I, I, I, P],
     "tk_moe_route": [P, L, I, I, I, F, I, P, P, P, P],
     "tk_moe_sort": [P, I, I, I, I, I, P, P, P, P],
     "tk_gemm_grouped_tile": [],
     "tk_gemm_grouped_simt": [P, L, L, P, P, L, L, P, P, L, L, I, I, I, I, I, I, P],
-    "tk_gemm_grouped_mma": [P, L, L, P, P, L, L, P, P, L, L, I, I, I, I, I, P],
+    "tk_gemm_grouped_mma": [P, L, L, P, P, L, L, P, P, L, L, I, I, I, I, I, I, P, L, P],
     "tk_moe_combine": [P, P, P, P, P, P, I, I, I, I, P],
     "tk_relu2": [P, L, I, P],
 }

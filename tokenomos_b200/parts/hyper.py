@@ -65,6 +65,10 @@ class StreamReader:
         what the sublayer gets, in the storage type."""
         mix = writer.hc_mix if writer is not None else None
         out = writer.hc_out if writer is not None else None
+        if self.taps is not None and ctx.host.decode_only:
+            # every sequence brings one token: the convolution and its state ride in the same kernel
+            return ops.hc_mix_norm(streams, y, mix, out, self.hc_in, self.weight, self.eps, self.streams, self.store,
+                                   keep32=False, conv=(self.taps, state, ctx.seq_ctx, ctx.seq_slot))
         h = ops.hc_mix_norm(streams, y, mix, out, self.hc_in, self.weight, self.eps, self.streams, self.store,
                             keep32=self.taps is not None)
         if self.taps is None:

@@ -53,17 +53,26 @@ class LatentAttention:
         # per head, as the batched products read them: W_uk[h]^T as [kv_rank, dim] rows, W_uv[h] [v_dim, kv_rank]
         self.uk_t = uk.view(heads, dim, kv_rank).transpose(1, 2).contiguous()
         self.uv = uv.view(heads, v_dim, kv_rank).contiguous()
+        # whether the second batched product takes the tensor-core form, which has the gate in its epilogue
+        self.fused_gate = kv_rank % 8 == 0 and v_dim % 8 == 0
         if o.in_features != heads * v_dim:
             raise ValueError("latent attention: the output projection does not match the value heads")
 
     def state_specs(self) -> dict:
         return {"kv": LatentKV(self.kv_rank + self.rot_dim, self.window)}
 
-    def _batched(self, a: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-        """``out[h] = a[h] @ w[h].T``: the library's batched product in 16 bits, the CUDA-core one in 32."""
-        if a.dtype == torch.float32:
-            return ops.gemm_batched(a, w)
-        return torch.bmm(a, w.transpose(1, 2))
+
+    def decode_splits(self, ctx: StepContext, per_tile: int, dtype: torch.dtype) -> int:
+        """How many CTAs share a decoded token's keys: in a step of single tokens each token is a
+        tile of its own, and a few of them behind long contexts would leave most of the GPU idle.
+        As many as put two CTAs on every SM, each with at least four key tiles of 64."""
+        if not (ctx.host.decode_only and ops.attention_latent_mma_supported(self.dim, self.kv_rank, self.rot_dim, dtype)):
+            return 1
+        longest = ctx.host.longest if self.window is None else min(ctx.host.longest, self.window)
+        key_tiles = -(-max(1, longest) // 64) + 1
+        chunks = -(-self.heads // min(self.heads, max(1, 32 // per_tile)))
+        ctas = max(1, ctx.n_tokens * chunks)
+        return max(1, min(-(-key_tiles // 4), 16, (2 * self.tuning.sm_count) // ctas))
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T, H = x.shape[0], self.heads
@@ -75,14 +84,20 @@ class LatentAttention:
         q = self.uq(cq)
         ops.latent_rotate_q(q, self.freq, ctx.positions, H, self.dim, self.rot_dim)
         q_nope = q.view(T, H, self.dim + self.rot_dim)[:, :, :self.dim].transpose(0, 1)      # [H, T, dim]
-        q_lat = self._batched(q_nope, self.uk_t)                                             # [H, T, kv_rank]
+        q_lat = ops.gemm_batched(q_nope, self.uk_t)                                          # [H, T, kv_rank]
         per_tile = ops.attention_latent_tokens(H, self.dim, self.kv_rank, self.rot_dim, q.dtype)
         _, tok0, _, ntok = ctx.tiles(per_tile)
         lat = ops.attention_latent(q_lat, q, cache, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile, H,
-                                   self.dim, self.rot_dim, self.window, self.scale)           # [H, T, kv_rank]
-        heads_out = self._batched(lat, self.uv)                                              # [H, T, v_dim]
+                                   self.dim, self.rot_dim, self.window, self.scale,
+                                   nsplit=self.decode_splits(ctx, per_tile, q.dtype))         # [H, T, kv_rank]
         n = self.q_rank + self.kv_rank + self.rot_dim
-        out = ops.head_gate_transpose(heads_out, proj[:, n:n + H] if self.gated else None)   # [T, H, v_dim]
+        gate = proj[:, n:n + H] if self.gated else None
+        if self.fused_gate and lat.dtype == torch.bfloat16:
+            # the values' up-projection writes [T, H, v_dim] itself and applies the gate as it does
+            out = torch.empty(T, H, self.v_dim, dtype=lat.dtype, device=lat.device)
+            ops.gemm_batched(lat, self.uv, out=out.transpose(0, 1), gate=gate)
+        else:
+            out = ops.head_gate_transpose(ops.gemm_batched(lat, self.uv), gate)              # [T, H, v_dim]
         return self.o(out.view(T, H * self.v_dim))
 
 

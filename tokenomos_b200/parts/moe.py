@@ -14,6 +14,8 @@ launches are the same whatever the routing, so a step can be recorded.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from tokenomos_b200 import ops
@@ -26,8 +28,8 @@ class RoutedExperts:
 
     def __init__(self, router: Linear, up: torch.Tensor, down: torch.Tensor, top: int, scale: float,
                  shared_up: Linear | None = None, shared_down: Linear | None = None, shared_gate: bool = False):
-        """``up`` [E, ff, width], ``down`` [E, width, ff]; ``router`` [E (+ 1 if ``shared_gate``), width]
-        in float32."""
+        """``up`` [E, ff, width], ``down`` [E, width, ff]; ``router`` [E (+ 1 if ``shared_gate``) (+ zero
+        rows), width]."""
         self.router, self.up, self.down = router, up.contiguous(), down.contiguous()
         self.experts, self.ff, self.width = up.shape
         self.top, self.scale = int(top), float(scale)
@@ -38,17 +40,19 @@ class RoutedExperts:
         if (shared_up is None) != (shared_down is None) or (shared_gate and shared_up is None):
             raise ValueError("mixture of experts: a shared expert has both projections; its gate needs it")
         self.shared_up, self.shared_down, self.shared_gate = shared_up, shared_down, bool(shared_gate)
-        if router.out_features != self.experts + (1 if shared_gate else 0):
+        if router.out_features < self.experts + (1 if shared_gate else 0):
             raise ValueError("mixture of experts: the router does not match the expert count")
-        self.tile = ops.gemm_grouped_tile()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         z = self.router(x, out_dtype=torch.float32)
         idx, w, gate = ops.moe_route(z, self.experts, self.top, self.scale, self.shared_gate)
-        row_token, pair_row, tile_expert = ops.moe_sort(idx, self.experts, self.tile)
+        # (both products, [ff, width] and [width, ff], must take the tile: the common divisor stands for both sizes)
+        tile = ops.gemm_grouped_tiles(x.dtype, math.gcd(self.ff, self.width), math.gcd(self.ff, self.width),
+                                      x.shape[0] * self.top)
+        row_token, pair_row, tile_expert = ops.moe_sort(idx, self.experts, tile)
         rows = row_token.numel()
-        act = ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, act=True)
-        y = ops.gemm_grouped(act, self.down, tile_expert, None, rows)
+        act = ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, act=True, tile=tile)
+        y = ops.gemm_grouped(act, self.down, tile_expert, None, rows, tile=tile)
         shared = None
         if self.shared_up is not None:
             shared = self.shared_down(ops.relu2(self.shared_up(x)))
@@ -60,10 +64,16 @@ def build_routed_experts(params: dict, tensors: dict, rt: Runtime) -> RoutedExpe
     n = params["experts"]
     up = torch.stack([tensors[f"e{i}.up"] for i in range(n)])
     down = torch.stack([tensors[f"e{i}.down"] for i in range(n)])
-    rows = [tensors["router"].float()]
+    # the router's rows (and the shared expert's gate row after them) in the model's storage type: a
+    # 16-bit model forms their products from 16-bit operands with 32-bit sums and a 32-bit result,
+    # like every other product of its input; a 32-bit model keeps them 32-bit
+    rows = [tensors["router"].to(rt.dtype)]
     gate = tensors.get("shared_gate")
     if gate is not None:
-        rows.append(gate.float().reshape(1, -1))
+        rows.append(gate.to(rt.dtype).reshape(1, -1))
+    pad = -sum(r.shape[0] for r in rows) % 8
+    if pad:
+        rows.append(rows[0].new_zeros(pad, rows[0].shape[1]))
     router = Linear(torch.cat(rows), tuning=rt.tuning)
     shared_up = Linear(tensors["shared_up"], tuning=rt.tuning) if "shared_up" in tensors else None
     shared_down = Linear(tensors["shared_down"], tuning=rt.tuning) if "shared_down" in tensors else None
