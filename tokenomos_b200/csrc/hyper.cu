@@ -135,9 +135,30 @@ hc_mix_norm_kernel(float* streams, const T* y, int64_t y_stride, const float* __
     if (taps != nullptr && K > 1) {
         const int ctx = seq_ctx[t];
         st = state + (size_t)TK_SLOT(TK_K_HYPER, seq_slot[t]) * (K - 1) * width;
-        for (int r = 0; r < K - 1; ++r) {
-            const bool live = ctx - (K - 1) + r >= 0;      // rows of positions before the sequence's start read as zeros
-            for (int i = threadIdx.x; i < width; i += blockDim.x) old_s[r * width + i] = live ? st[(size_t)r * width + i] : 0.f;
+        // (all of a thread's loads are asked for before the first is used; rows of positions before
+        // the sequence's start read as zeros)
+        if constexpr (VEC) {
+            for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+                float4 tmp[MAX_TAPS - 1];
+#pragma unroll
+                for (int r = 0; r < MAX_TAPS - 1; ++r)
+                    if (r < K - 1)
+                        tmp[r] = ctx - (K - 1) + r >= 0 ? *reinterpret_cast<const float4*>(st + (size_t)r * width + i)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int r = 0; r < MAX_TAPS - 1; ++r)
+                    if (r < K - 1) *reinterpret_cast<float4*>(old_s + r * width + i) = tmp[r];
+            }
+        } else {
+            for (int i = threadIdx.x; i < width; i += blockDim.x) {
+                float tmp[MAX_TAPS - 1];
+#pragma unroll
+                for (int r = 0; r < MAX_TAPS - 1; ++r)
+                    if (r < K - 1) tmp[r] = ctx - (K - 1) + r >= 0 ? st[(size_t)r * width + i] : 0.f;
+#pragma unroll
+                for (int r = 0; r < MAX_TAPS - 1; ++r)
+                    if (r < K - 1) old_s[r * width + i] = tmp[r];
+            }
         }
     }
     if constexpr (VEC) {
@@ -215,7 +236,7 @@ hc_mix_norm_kernel(float* streams, const T* y, int64_t y_stride, const float* __
     const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
     if (taps != nullptr) {
         // row t is sequence t's only token; rows of the state: positions ctx - (K - 1) .. ctx - 1
-        // (each thread reads and writes the same channels of old_s that it filled above)
+        // (old_s was filled before the sum's barriers)
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
             const float v = u_s[i] * rstd * norm_w[i];
             const float* w = taps + (size_t)i * K;

@@ -30,8 +30,10 @@ __device__ __forceinline__ float rotated(const T* src, int c, int rot, const flo
     return (c & 1) ? x * cs[i] + y * sn[i] : x * cs[i] - y * sn[i];
 }
 
+// grid (tokens, 2): block (t, 0) norms the query latent, block (t, 1) norms the key/value latent,
+// rotates the shared key part and writes both into the cache
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 latent_prepare_kernel(const T* proj, int64_t proj_stride, const float* __restrict__ wq,
                       const float* __restrict__ wkv, float eps, const float* __restrict__ freq,
                       const int* positions, const int* tok_seq, const int* block_table, int bt_stride,
@@ -40,27 +42,31 @@ latent_prepare_kernel(const T* proj, int64_t proj_stride, const float* __restric
     pdl_wait();
     extern __shared__ float smem[];
     __shared__ float red[33];
+    const int t = blockIdx.x;
+    const T* row = proj + (size_t)t * proj_stride;
+    if (blockIdx.y == 0) {
+        if (Rq == 0) return;
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < Rq; i += blockDim.x) {
+            const float v = to_f<T>(row[i]);
+            ss += v * v;
+        }
+        const float rq = 1.0f / sqrtf(block_sum(ss, red) / (float)Rq + eps);
+        for (int i = threadIdx.x; i < Rq; i += blockDim.x)
+            cq_out[(size_t)t * Rq + i] = from_f<T>(to_f<T>(row[i]) * rq * wq[i]);
+        return;
+    }
     float* cs = smem;
     float* sn = smem + rot / 2;
-    const int t = blockIdx.x;
     const int pos = positions[t];
+    const int page = TK_PAGE(TK_K_LATENT, block_table[(size_t)tok_seq[t] * bt_stride + pos / P]);
     for (int i = threadIdx.x; i < rot / 2; i += blockDim.x) sincosf((float)pos * freq[i], &sn[i], &cs[i]);
-    const T* row = proj + (size_t)t * proj_stride;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < Rq; i += blockDim.x) {
-        const float v = to_f<T>(row[i]);
-        ss += v * v;
-    }
-    const float rq = Rq > 0 ? 1.0f / sqrtf(block_sum(ss, red) / (float)Rq + eps) : 0.f;
-    for (int i = threadIdx.x; i < Rq; i += blockDim.x)
-        cq_out[(size_t)t * Rq + i] = from_f<T>(to_f<T>(row[i]) * rq * wq[i]);
-    ss = 0.f;
     for (int i = threadIdx.x; i < R; i += blockDim.x) {
         const float v = to_f<T>(row[Rq + i]);
         ss += v * v;
     }
     const float rk = 1.0f / sqrtf(block_sum(ss, red) / (float)R + eps);   // (its barriers also publish cs / sn)
-    const int page = TK_PAGE(TK_K_LATENT, block_table[(size_t)tok_seq[t] * bt_stride + pos / P]);
     T* dst = cache + ((size_t)page * P + pos % P) * (R + Dr);
     for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = from_f<T>(to_f<T>(row[Rq + i]) * rk * wkv[i]);
     for (int i = threadIdx.x; i < Dr; i += blockDim.x) dst[R + i] = from_f<T>(rotated<T>(row + Rq + R, i, rot, cs, sn));
@@ -75,11 +81,11 @@ TK_API int tk_latent_prepare(const void* proj, int64_t proj_stride, const float*
     if (tokens == 0) return 0;
     const size_t smem = (size_t)(rot + 2) * sizeof(float);
     if (dtype == TK_F32)
-        tk_launch(latent_prepare_kernel<float>, dim3(tokens), dim3(256), smem, stream, (const float*)proj,
+        tk_launch(latent_prepare_kernel<float>, dim3(tokens, 2), dim3(128), smem, stream, (const float*)proj,
                   proj_stride, wq, wkv, eps, freq, positions, tok_seq, block_table, bt_stride, (float*)cq_out,
                   (float*)cache, Rq, R, Dr, rot, P);
     else if (dtype == TK_BF16)
-        tk_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(tokens), dim3(256), smem, stream,
+        tk_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(tokens, 2), dim3(128), smem, stream,
                   (const __nv_bfloat16*)proj, proj_stride, wq, wkv, eps, freq, positions, tok_seq, block_table,
                   bt_stride, (__nv_bfloat16*)cq_out, (__nv_bfloat16*)cache, Rq, R, Dr, rot, P);
     else

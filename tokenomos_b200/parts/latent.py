@@ -65,14 +65,14 @@ class LatentAttention:
     def decode_splits(self, ctx: StepContext, per_tile: int, dtype: torch.dtype) -> int:
         """How many CTAs share a decoded token's keys: in a step of single tokens each token is a
         tile of its own, and a few of them behind long contexts would leave most of the GPU idle.
-        As many as put two CTAs on every SM, each with at least four key tiles of 64."""
+        As many as put two CTAs on every SM, each with at least two key tiles of 64."""
         if not (ctx.host.decode_only and ops.attention_latent_mma_supported(self.dim, self.kv_rank, self.rot_dim, dtype)):
             return 1
         longest = ctx.host.longest if self.window is None else min(ctx.host.longest, self.window)
         key_tiles = -(-max(1, longest) // 64) + 1
         chunks = -(-self.heads // min(self.heads, max(1, 32 // per_tile)))
         ctas = max(1, ctx.n_tokens * chunks)
-        return max(1, min(-(-key_tiles // 4), 16, (2 * self.tuning.sm_count) // ctas))
+        return max(1, min(-(-key_tiles // 2), 16, (2 * self.tuning.sm_count) // ctas))
 
     def forward(self, x: torch.Tensor, ctx: StepContext, call: int) -> torch.Tensor:
         T, H = x.shape[0], self.heads
