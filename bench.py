@@ -1225,9 +1225,19 @@ def laposun_kernels(z: dict, pk: dict) -> list[dict]:
 
     wd = torch.randn(top * ff, W, device=dev).to(bf) * 0.02
     wd2 = torch.randn(W, top * ff, device=dev).to(bf) * 0.02
-    add("experts: two grouped products", _timed_us(experts, flush, reps=5),
-        _timed_us(lambda: F.linear(F.linear(x, wd), wd2), flush), 4.0 * T * top * ff * W, 4.0 * T * top * ff * W, "flops",
-        "library product of equal flops")
+    dense_us = _timed_us(lambda: F.linear(F.linear(x, wd), wd2), flush)
+    add("experts: two grouped products, own mma.sync kernel (steps below 1,024 rows)", _timed_us(experts, flush, reps=5),
+        dense_us, 4.0 * T * top * ff * W, 4.0 * T * top * ff * W, "flops", "library product of equal flops")
+    if hasattr(torch, "_grouped_mm"):
+        r8, p8, _, ends = ops.moe_sort(idx, E, 8, ends=True)
+
+        def experts_library():
+            a = ops.relu2(torch._grouped_mm(ops.gather_rows_or_zero(x, r8), up.transpose(1, 2), offs=ends))
+            return torch._grouped_mm(a, down.transpose(1, 2), offs=ends)
+
+        add("experts: gather + two grouped products of the library + activation (as a 2,048-token step runs)",
+            _timed_us(experts_library, flush, reps=5), dense_us, 4.0 * T * top * ff * W, 4.0 * T * top * ff * W, "flops",
+            "library product of equal flops")
     yy = experts()
     shared = torch.randn(T, W, device=dev).to(bf)
 

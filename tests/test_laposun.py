@@ -570,7 +570,7 @@ def test_batched_and_grouped_products():
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("E, top, shared, T", [(6, 2, 48, 37), (5, 1, 0, 9), (4, 4, 16, 70), (40, 7, 8, 3),
-                                               (3, 2, 0, 1)])
+                                               (3, 2, 0, 1), (9, 2, 16, 600)])      # the last: the library's grouped product
 def test_routed_experts_alone(dtype, E, top, shared, T):
     from tokenomos_b200.parts.registry import Runtime, builder_of
 

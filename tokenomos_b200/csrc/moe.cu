@@ -90,10 +90,10 @@ TK_API int tk_moe_route(const float* logits, int64_t ld, int tokens, int E, int 
 
 // One block. row_token[cap_rows]: the token whose input a row of the sorted layout reads (-1:
 // padding); pair_row[pairs]: where pair (token * top + k) sits; tile_expert[cap_rows / tile]: the
-// expert of each tile (-1: unused).
+// expert of each tile (-1: unused); expert_end[E] (optional): the row after each expert's block.
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* idx, int pairs, int top, int E, int tile, int cap_rows, int* row_token, int* pair_row,
-                int* tile_expert) {
+                int* tile_expert, int* expert_end) {
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ int ism[];
@@ -112,6 +112,7 @@ moe_sort_kernel(const int* idx, int pairs, int top, int E, int tile, int cap_row
             const int tiles = (count[e] + tile - 1) / tile;
             for (int k = 0; k < tiles; ++k) tile_expert[at / tile + k] = e;
             at += tiles * tile;
+            if (expert_end != nullptr) expert_end[e] = at;      // where the expert's padded block ends
         }
         for (int k = at / tile; k < cap_rows / tile; ++k) tile_expert[k] = -1;
     }
@@ -125,14 +126,14 @@ moe_sort_kernel(const int* idx, int pairs, int top, int E, int tile, int cap_row
 }
 
 TK_API int tk_moe_sort(const int* idx, int pairs, int top, int E, int tile, int cap_rows, int* row_token,
-                       int* pair_row, int* tile_expert, cudaStream_t stream) {
+                       int* pair_row, int* tile_expert, int* expert_end, cudaStream_t stream) {
     TK_CHECK_ARG(pairs >= 0 && top > 0 && E > 0 && tile > 0, "moe_sort: bad sizes");
     TK_CHECK_ARG(cap_rows % tile == 0 && cap_rows >= pairs + (E < pairs ? E : pairs) * (tile - 1),
                  "moe_sort: %d rows cannot hold %d pairs of %d experts in tiles of %d", cap_rows, pairs, E, tile);
     TK_CHECK_ARG((size_t)E * 12 <= 48 * 1024, "moe_sort: %d experts do not fit shared memory", E);
     if (pairs == 0) return 0;
     tk_launch(moe_sort_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int), stream, idx, pairs, top, E, tile,
-              cap_rows, row_token, pair_row, tile_expert);
+              cap_rows, row_token, pair_row, tile_expert, expert_end);
     TK_CHECK_LAUNCH("moe_sort");
     return 0;
 }
@@ -472,5 +473,40 @@ TK_API int tk_gemm_grouped_mma(const void* A, int64_t lda, int64_t a_gs, const i
     else TK_GG(128, 4);
 #undef TK_GG
     TK_CHECK_LAUNCH("gemm_grouped_mma");
+    return 0;
+}
+
+// out[r] = index[r] >= 0 ? table[index[r]] : 0  (bfloat16 or float rows): the experts' input rows in
+// the sorted layout, for a product that cannot gather by itself
+template <typename T>
+__global__ void gather_rows_or_zero_kernel(const T* table, const int* index, T* out, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int src = index[r];
+    T* dst = out + (size_t)r * width;
+    constexpr int VEC = 16 / sizeof(T);
+    if (width % VEC == 0) {
+        const uint4* s4 = src >= 0 ? reinterpret_cast<const uint4*>(table + (size_t)src * width) : nullptr;
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < width / VEC; i += blockDim.x) d4[i] = s4 != nullptr ? s4[i] : make_uint4(0, 0, 0, 0);
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = src >= 0 ? table[(size_t)src * width + i] : from_f<T>(0.f);
+    }
+}
+
+TK_API int tk_gather_rows_or_zero(const void* table, const int* index, void* out, int rows, int width, int dtype,
+                                  cudaStream_t stream) {
+    TK_CHECK_ARG(rows >= 0 && width > 0, "gather_rows_or_zero: bad sizes");
+    if (rows == 0) return 0;
+    if (dtype == TK_F32)
+        tk_launch(gather_rows_or_zero_kernel<float>, dim3(rows), dim3(128), 0, stream, (const float*)table, index,
+                  (float*)out, width);
+    else if (dtype == TK_BF16)
+        tk_launch(gather_rows_or_zero_kernel<__nv_bfloat16>, dim3(rows), dim3(128), 0, stream,
+                  (const __nv_bfloat16*)table, index, (__nv_bfloat16*)out, width);
+    else
+        TK_CHECK_ARG(false, "gather_rows_or_zero: unknown dtype %d", dtype);
+    TK_CHECK_LAUNCH("gather_rows_or_zero");
     return 0;
 }

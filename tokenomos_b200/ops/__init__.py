@@ -1020,10 +1020,11 @@ def gemm_grouped_tile() -> int:
     return _lib.call("tk_gemm_grouped_tile")
 
 
-def moe_sort(idx: torch.Tensor, experts: int, tile: int):
+def moe_sort(idx: torch.Tensor, experts: int, tile: int, ends: bool = False):
     """(token, k) pairs grouped by expert, each expert's rows padded to whole tiles:
     ``row_token`` [rows] (-1: padding), ``pair_row`` [T * top], ``tile_expert`` [rows / tile] (-1: unused).
-    ``rows`` is the bound ``T * top + min(experts, T * top) * (tile - 1)`` rounded up to whole tiles."""
+    ``rows`` is the bound ``T * top + min(experts, T * top) * (tile - 1)`` rounded up to whole tiles.
+    ``ends``: also ``expert_end`` [experts] (int32), the row after each expert's padded block."""
     _cuda(idx)
     T, top = idx.shape
     pairs = T * top
@@ -1031,9 +1032,23 @@ def moe_sort(idx: torch.Tensor, experts: int, tile: int):
     row_token = torch.empty(cap, dtype=torch.int32, device=idx.device)
     pair_row = torch.empty(pairs, dtype=torch.int32, device=idx.device)
     tile_expert = torch.empty(cap // tile, dtype=torch.int32, device=idx.device)
+    expert_end = torch.empty(experts, dtype=torch.int32, device=idx.device) if ends else None
     _lib.call("tk_moe_sort", _ptr(_i32(idx, "idx")), pairs, top, int(experts), int(tile), cap, _ptr(row_token),
-              _ptr(pair_row), _ptr(tile_expert), _stream())
+              _ptr(pair_row), _ptr(tile_expert), _ptr(expert_end), _stream())
+    if ends:
+        return row_token, pair_row, tile_expert, expert_end
     return row_token, pair_row, tile_expert
+
+
+def gather_rows_or_zero(table: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """``out[r] = table[index[r]]``, a row of zeros where ``index[r]`` is negative."""
+    _cuda(table, index)
+    if not table.is_contiguous():
+        raise KernelError("gather_rows_or_zero: the table must be contiguous")
+    out = torch.empty(index.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _lib.call("tk_gather_rows_or_zero", _ptr(table), _ptr(_i32(index, "index")), _ptr(out), index.numel(),
+              table.shape[1], _dtype_code(table), _stream())
+    return out
 
 
 def gemm_grouped_tiles(a_dtype: torch.dtype, n: int, k: int, rows: int) -> int:

@@ -82,7 +82,8 @@ _SIGNATURES = {
     "tk_attn_latent_merge": [P, P, P, I, I, I, P],
     "tk_head_gate_transpose": [P, P, L, P, I, I, I, I, P],
     "tk_moe_route": [P, L, I, I, I, F, I, P, P, P, P],
-    "tk_moe_sort": [P, I, I, I, I, I, P, P, P, P],
+    "tk_moe_sort": [P, I, I, I, I, I, P, P, P, P, P],
+    "tk_gather_rows_or_zero": [P, P, P, I, I, I, P],
     "tk_gemm_grouped_tile": [],
     "tk_gemm_grouped_simt": [P, L, L, P, P, L, L, P, P, L, L, I, I, I, I, I, I, P],
     "tk_gemm_grouped_mma": [P, L, L, P, P, L, L, P, P, L, L, I, I, I, I, I, I, P, L, P],

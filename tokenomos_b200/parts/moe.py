@@ -27,7 +27,8 @@ class RoutedExperts:
     capture_safe = True
 
     def __init__(self, router: Linear, up: torch.Tensor, down: torch.Tensor, top: int, scale: float,
-                 shared_up: Linear | None = None, shared_down: Linear | None = None, shared_gate: bool = False):
+                 shared_up: Linear | None = None, shared_down: Linear | None = None, shared_gate: bool = False,
+                 library_rows: int = 1024):
         """``up`` [E, ff, width], ``down`` [E, width, ff]; ``router`` [E (+ 1 if ``shared_gate``) (+ zero
         rows), width]."""
         self.router, self.up, self.down = router, up.contiguous(), down.contiguous()
@@ -40,12 +41,20 @@ class RoutedExperts:
         if (shared_up is None) != (shared_down is None) or (shared_gate and shared_up is None):
             raise ValueError("mixture of experts: a shared expert has both projections; its gate needs it")
         self.shared_up, self.shared_down, self.shared_gate = shared_up, shared_down, bool(shared_gate)
+        # from that many rows on the two grouped products are the library's, where it has one for
+        # these sizes (16-bit storage, sizes in whole 16-byte chunks)
+        self.library_rows = int(library_rows)
+        self.library = (hasattr(torch, "_grouped_mm") and up.dtype == torch.bfloat16 and self.ff % 8 == 0
+                        and self.width % 8 == 0)
         if router.out_features < self.experts + (1 if shared_gate else 0):
             raise ValueError("mixture of experts: the router does not match the expert count")
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         z = self.router(x, out_dtype=torch.float32)
         idx, w, gate = ops.moe_route(z, self.experts, self.top, self.scale, self.shared_gate)
+        if self.library and x.shape[0] * self.top >= self.library_rows:
+            y, pair_row = self._experts_library(x, idx)
+            return ops.moe_combine(y, pair_row, w, self._shared(x), gate)
         # (both products, [ff, width] and [width, ff], must take the tile: the common divisor stands for both sizes)
         tile = ops.gemm_grouped_tiles(x.dtype, math.gcd(self.ff, self.width), math.gcd(self.ff, self.width),
                                       x.shape[0] * self.top)
@@ -53,10 +62,20 @@ class RoutedExperts:
         rows = row_token.numel()
         act = ops.gemm_grouped(x, self.up, tile_expert, row_token, rows, act=True, tile=tile)
         y = ops.gemm_grouped(act, self.down, tile_expert, None, rows, tile=tile)
-        shared = None
-        if self.shared_up is not None:
-            shared = self.shared_down(ops.relu2(self.shared_up(x)))
-        return ops.moe_combine(y, pair_row, w, shared, gate)
+        return ops.moe_combine(y, pair_row, w, self._shared(x), gate)
+
+    def _shared(self, x: torch.Tensor) -> torch.Tensor | None:
+        if self.shared_up is None:
+            return None
+        return self.shared_down(ops.relu2(self.shared_up(x)))
+
+    def _experts_library(self, x: torch.Tensor, idx: torch.Tensor):
+        """The experts through the library's grouped product: the rows gathered into the sorted
+        layout, each expert's block of rows given by its end."""
+        row_token, pair_row, _, ends = ops.moe_sort(idx, self.experts, 8, ends=True)
+        rows = ops.gather_rows_or_zero(x, row_token)
+        act = ops.relu2(torch._grouped_mm(rows, self.up.transpose(1, 2), offs=ends))
+        return torch._grouped_mm(act, self.down.transpose(1, 2), offs=ends), pair_row
 
 
 @register("feed_forward", "relu2_moe")
@@ -77,4 +96,5 @@ def build_routed_experts(params: dict, tensors: dict, rt: Runtime) -> RoutedExpe
     router = Linear(torch.cat(rows), tuning=rt.tuning)
     shared_up = Linear(tensors["shared_up"], tuning=rt.tuning) if "shared_up" in tensors else None
     shared_down = Linear(tensors["shared_down"], tuning=rt.tuning) if "shared_down" in tensors else None
-    return RoutedExperts(router, up, down, params["top"], params["scale"], shared_up, shared_down, gate is not None)
+    return RoutedExperts(router, up, down, params["top"], params["scale"], shared_up, shared_down, gate is not None,
+                         library_rows=rt.tuning.grouped_library_rows)

@@ -51,6 +51,11 @@ class Tuning:
     it always is above ``skinny_rows`` rows.
     ``prefill_split_ctas_per_sm`` / ``prefill_split_scratch_mb``: how far a prompt portion's
     tiles may share their keys out over CTAs (``Attention.prefill_splits``).
+    ``grouped_library_rows``: from that many (token, expert) rows on, a mixture of experts' two
+    grouped products are the library's (``torch._grouped_mm`` over the sorted layout, 149 us against
+    435 us for the ``mma.sync`` kernel at 8,192 rows of 2,048 x 1,536); below, the framework's own
+    kernel, which gathers its rows, has the activation in its epilogue and chains with its
+    neighbours by programmatic dependent launch.
     ``conv_tile``: tokens of a conv tile; up to 16 the tiled kernel takes them (one thread per
     token and 8 channels, a 2,048-token portion of 2,048 channels at memory speed).
     ``fuse_norms``: 16-bit models fold each pre-norm's weight into the columns of the projection
@@ -78,6 +83,7 @@ class Tuning:
     decode_fused_carveout: int = 62
     prefill_split_ctas_per_sm: int = 2
     prefill_split_scratch_mb: int = 64
+    grouped_library_rows: int = 1024
     conv_tile: int = 16
     fuse_norms: bool = True
 
