@@ -313,7 +313,7 @@ TK_API int tk_relu2(void* x, int64_t n, int dtype, cudaStream_t stream) {
 // in whole 16-byte chunks and 16-byte aligned rows.
 // ---------------------------------------------------------------------------------------------
 namespace {
-constexpr int GN = 128, GK = 32, GLD = 40, G_THREADS = 256;
+constexpr int GK = 32, GLD = 40, G_THREADS = 256;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -338,7 +338,8 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], 
 
 // GM: rows of a tile (64: 8 warps of 32 x 32; 128: 8 warps of 64 x 32); GSTAGES: copies in flight.
 // gate (batched form only): C[g][m][:] *= sigmoid(gate[m * gate_stride + g]).
-template <int GM, int GSTAGES>
+// GN: columns of a tile (128, or 64 for steps of a few rows: twice the CTAs to stream the weights).
+template <int GM, int GSTAGES, int GN>
 __global__ void __launch_bounds__(G_THREADS)
 gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const int* row_index,
                         const __nv_bfloat16* __restrict__ W, int64_t ldw, int64_t w_gs, const int* tile_group,
@@ -351,6 +352,7 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
     __nv_bfloat16 (*Ws)[GN * GLD] = reinterpret_cast<__nv_bfloat16 (*)[GN * GLD]>(gsm + (size_t)GSTAGES * GM * GLD * 2);
     __shared__ int rows_s[GM];
     constexpr int MI = GM / 32;              // m16 blocks of a warp's tile
+    constexpr int NJ = GN / 32;              // n8 blocks of a warp's tile (its columns: GN / 4)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
     if (tile_group != nullptr) {
@@ -382,7 +384,7 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
                        av ? (const void*)(A + (size_t)a_src[i] * lda + k) : (const void*)A, av);
         }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < GN / 64; ++i) {
             const int r = (tid >> 2) + i * 64;
             const int n = n0 + r;
             const bool wv = n < N && k < K;
@@ -393,12 +395,12 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
         if (s < ktiles) load(s, s);
         cp_async_commit();
     }
-    const int wm = (warp >> 2) * (GM / 2), wn = (warp & 3) * 32;
-    float acc[MI][4][4];
+    const int wm = (warp >> 2) * (GM / 2), wn = (warp & 3) * (GN / 4);
+    float acc[MI][NJ][4];
 #pragma unroll
     for (int i = 0; i < MI; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < NJ; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
     for (int kt = 0; kt < ktiles; ++kt) {
@@ -410,17 +412,17 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
         const __nv_bfloat16* ws = Ws[kt % GSTAGES];
 #pragma unroll
         for (int kk = 0; kk < GK; kk += 16) {
-            unsigned a[MI][4], b[2][4];
+            unsigned a[MI][4], b[NJ / 2][4];
 #pragma unroll
             for (int i = 0; i < MI; ++i)
                 ldmatrix_x4(a[i], as + (wm + i * 16 + (lane & 15)) * GLD + kk + (lane >> 4) * 8);
 #pragma unroll
-            for (int j = 0; j < 2; ++j)
+            for (int j = 0; j < NJ / 2; ++j)
                 ldmatrix_x4(b[j], ws + (wn + j * 16 + (lane & 7) + (lane >> 4) * 8) * GLD + kk + ((lane >> 3) & 1) * 8);
 #pragma unroll
             for (int i = 0; i < MI; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) mma_bf16(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
+                for (int j = 0; j < NJ; ++j) mma_bf16(acc[i][j], a[i], b[j >> 1][(j & 1) * 2], b[j >> 1][(j & 1) * 2 + 1]);
         }
     }
     cp_async_wait<0>();
@@ -432,7 +434,7 @@ gemm_grouped_mma_kernel(const __nv_bfloat16* A, int64_t lda, int64_t a_gs, const
             if (m >= M) continue;
             const float gv = gate != nullptr ? 1.0f / (1.0f + expf(-__bfloat162float(gate[(size_t)m * gate_stride + gz]))) : 1.0f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
+            for (int j = 0; j < NJ; ++j) {
                 const int n = n0 + wn + j * 8 + (lane & 3) * 2;
                 if (n >= N) continue;
                 float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
@@ -460,17 +462,25 @@ TK_API int tk_gemm_grouped_mma(const void* A, int64_t lda, int64_t a_gs, const i
                  "gemm_grouped_mma: operands must be 16-byte aligned");
     TK_CHECK_ARG(act == 0 || act == 1, "gemm_grouped_mma: activation %d", act);
     if (M == 0) return 0;
-    dim3 grid((N + GN - 1) / GN, (M + tile_rows - 1) / tile_rows, tile_group != nullptr ? 1 : groups);
-#define TK_GG(GMV, ST)                                                                                              \
+    // few row tiles (a step of a few tokens streams the weights): columns in tiles of 64, so that
+    // twice as many CTAs share the stream and an SM holds four of them
+    const int m_tiles = (M + tile_rows - 1) / tile_rows;
+    const int groups_z = tile_group != nullptr ? 1 : groups;
+    const bool narrow = tile_rows == 64 && (long long)m_tiles * groups_z * ((N + 127) / 128) <= 2 * 148;
+    const int gn = narrow ? 64 : 128;
+    dim3 grid((N + gn - 1) / gn, m_tiles, groups_z);
+#define TK_GG(GMV, ST, GNV)                                                                                         \
     do {                                                                                                            \
-        const size_t smem = (size_t)ST * (GMV + GN) * GLD * 2;                                                      \
-        cudaFuncSetAttribute(gemm_grouped_mma_kernel<GMV, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        tk_launch(gemm_grouped_mma_kernel<GMV, ST>, grid, dim3(G_THREADS), smem, stream, (const __nv_bfloat16*)A, lda, \
-                  a_gs, row_index, (const __nv_bfloat16*)W, ldw, w_gs, tile_group, (__nv_bfloat16*)C, ldc, c_gs, M, N, \
-                  K, act, (const __nv_bfloat16*)gate, gate_stride);                                                 \
+        const size_t smem = (size_t)ST * (GMV + GNV) * GLD * 2;                                                     \
+        cudaFuncSetAttribute(gemm_grouped_mma_kernel<GMV, ST, GNV>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                             (int)smem);                                                                            \
+        tk_launch(gemm_grouped_mma_kernel<GMV, ST, GNV>, grid, dim3(G_THREADS), smem, stream,                       \
+                  (const __nv_bfloat16*)A, lda, a_gs, row_index, (const __nv_bfloat16*)W, ldw, w_gs, tile_group,    \
+                  (__nv_bfloat16*)C, ldc, c_gs, M, N, K, act, (const __nv_bfloat16*)gate, gate_stride);             \
     } while (0)
-    if (tile_rows == 64) TK_GG(64, 5);
-    else TK_GG(128, 4);
+    if (narrow) TK_GG(64, 6, 64);
+    else if (tile_rows == 64) TK_GG(64, 5, 128);
+    else TK_GG(128, 4, 128);
 #undef TK_GG
     TK_CHECK_LAUNCH("gemm_grouped_mma");
     return 0;
