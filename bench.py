@@ -1201,8 +1201,8 @@ def laposun_kernels(z: dict, pk: dict) -> list[dict]:
     nt1 = torch.ones_like(t01)
     dqd, doutd = qd[:B].contiguous(), torch.empty_like(qd[:B])
     add("decode attention over the latent cache, 64 tokens",
-        _timed_us(lambda: ops.attention_latent(dq_lat, dq, cache, dpos, dseq, dtbl, t01, nt1, per, H, D, Dr, win, 0.1,
-                                               nsplit=4), flush),
+        _timed_us(lambda: ops.attention_latent(dq_lat, dq, cache, dpos, dseq, dtbl, t01, nt1, 1, H, D, Dr, win, 0.1,
+                                               nsplit=4, rows16=True), flush),
         _timed_us(lambda: ops.attention_decode_mma(dqd, pool, doutd, dpos, dseq, dtbl, None, win, D ** -0.5, 2,
                                                    gate_e[:B], 4, True, True), flush),
         B * keys * (R + Dr) * 2, B * G * keys * D * 2 * 2, "bytes", "Darizen: decode attention")

@@ -452,10 +452,13 @@ class LatentSequence:
         ops.latent_rotate_q(qq, self.freq, ctx.positions, self.H, self.D, self.Dr)
         q_lat = q[a:b, :, :self.R].transpose(0, 1).to(self.dtype).cuda().contiguous()       # D >= R in these tests
         per_tile = ops.attention_latent_tokens(self.H, self.D, self.R, self.Dr, self.dtype)
+        if b - a == 1:
+            per_tile = 1          # a single token: the 16-row form where the tensor-core kernel runs
         _, tok0, _, ntok = ctx.tiles(per_tile)
         # (a single token's keys shared out over three CTAs where the tensor-core form runs)
         out = ops.attention_latent(q_lat, qq, cache, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile,
-                                   self.H, self.D, self.Dr, window, scale, nsplit=3 if b - a == 1 else 1)
+                                   self.H, self.D, self.Dr, window, scale, nsplit=3 if b - a == 1 else 1,
+                                   rows16=b - a == 1 and per_tile == 1)
         self.hs.commit([("x", [0] * (b - a))])
         return out.transpose(0, 1).double().cpu()
 

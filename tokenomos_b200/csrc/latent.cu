@@ -385,7 +385,11 @@ __device__ __forceinline__ void a_mma_bf16(float (&c)[4], const unsigned (&a)[4]
 }
 }  // namespace
 
-template <int MAXNB>       // n8 blocks of the output a warp may hold: R / 32 <= MAXNB
+// MAXNB: n8 blocks of the output a warp may hold. RG: row groups of 16 rows a CTA takes: 2 (32 rows,
+// four warps a group: 16 keys each in the score phase, R / 4 columns each in the output phase) or 1
+// (16 rows, all eight warps on them: 8 keys and R / 8 columns each; for steps of single tokens,
+// whose tiles are one token's heads).
+template <int MAXNB, int RG>
 __global__ void __launch_bounds__(A_THREADS, 1)
 attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const __nv_bfloat16* cache,
                        __nv_bfloat16* out, const int* positions, const int* tok_seq, const int* block_table,
@@ -395,12 +399,16 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
     pdl_launch_dependents();
     pdl_wait();
     extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int NQ = 8 / RG;               // warps of a row group
+    constexpr int AMR = 16 * RG;             // rows of the CTA
+    constexpr int KW = AN / NQ;              // keys a warp scores
+    constexpr int NJS = KW / 8;              // n8 blocks of those
     const int DK = R + Dr, KLD = DK + 8;
-    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [AM][KLD]
-    __nv_bfloat16* Ks = Qs + AM * KLD;                                       // [2][AN][KLD]
-    __nv_bfloat16* Ps = Ks + 2 * AN * KLD;                                   // [AM][PLD]
-    float* red_max = reinterpret_cast<float*>(Ps + AM * PLD);                // [2 row groups][4][16]
-    float* red_sum = red_max + 128;                                          // [2][4][16]
+    __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);          // [AMR][KLD]
+    __nv_bfloat16* Ks = Qs + AMR * KLD;                                      // [2][AN][KLD]
+    __nv_bfloat16* Ps = Ks + 2 * AN * KLD;                                   // [AMR][PLD]
+    float* red_max = reinterpret_cast<float*>(Ps + AMR * PLD);               // [8 warps][16]
+    float* red_sum = red_max + 128;                                          // [8 warps][16]
     __shared__ int row_pos[AM];
 
     const int g0 = blockIdx.y * heads_per_chunk;
@@ -411,12 +419,12 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
     const int rows = ntok * gh;
     const int seq = tok_seq[tok0];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int rg = warp >> 2, wq = warp & 3;
+    const int rg = warp / NQ, wq = warp % NQ;
     const int chunks = DK / 8;
 
-    if (tid < AM) row_pos[tid] = tid < rows ? positions[tok0 + tid / gh] : -1;
+    if (tid < AMR) row_pos[tid] = tid < rows ? positions[tok0 + tid / gh] : -1;
     // the queries: [q in the latent's space | rotated part], rows beyond the tile's are zero
-    for (int c = tid; c < AM * chunks; c += A_THREADS) {
+    for (int c = tid; c < AMR * chunks; c += A_THREADS) {
         const int r = c / chunks, ch = c % chunks;
         const bool valid = r < rows;
         const void* src = q_lat;
@@ -459,8 +467,8 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
     float acc[MAXNB][4];
 #pragma unroll
     for (int j = 0; j < MAXNB; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
-    const int nb = R / 32;                  // n8 blocks of my column quarter
-    const int col0 = wq * (R / 4);
+    const int nb = R / (8 * NQ);            // n8 blocks of my share of the columns
+    const int col0 = wq * (R / NQ);
 
     for (int it = it_begin; it < n_it; ++it) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -472,19 +480,41 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         {
             const __nv_bfloat16* qa = Qs + (rg * 16 + (lane & 15)) * KLD + (lane >> 4) * 8;
-            const __nv_bfloat16* kb = ks + (wq * 16 + (lane & 7) + (lane >> 4) * 8) * KLD + ((lane >> 3) & 1) * 8;
-            for (int k = 0; k < DK; k += 16) {
-                unsigned a[4], b[4];
-                a_ldmatrix_x4(a, qa + k);
-                a_ldmatrix_x4(b, kb + k);
-                a_mma_bf16(s[0], a, b[0], b[1]);
-                a_mma_bf16(s[1], a, b[2], b[3]);
+            if constexpr (NJS == 2) {
+                const __nv_bfloat16* kb = ks + (wq * 16 + (lane & 7) + (lane >> 4) * 8) * KLD + ((lane >> 3) & 1) * 8;
+                for (int k = 0; k < DK; k += 16) {
+                    unsigned a[4], b[4];
+                    a_ldmatrix_x4(a, qa + k);
+                    a_ldmatrix_x4(b, kb + k);
+                    a_mma_bf16(s[0], a, b[0], b[1]);
+                    a_mma_bf16(s[1], a, b[2], b[3]);
+                }
+            } else {
+                // 8 keys a warp: their K steps two at a time (one ldmatrix brings k .. k + 31 of the 8 keys)
+                const __nv_bfloat16* kb = ks + (wq * 8 + (lane & 7)) * KLD + (lane >> 3) * 8;
+                int k = 0;
+                for (; k + 32 <= DK; k += 32) {
+                    unsigned a0[4], a1[4], b[4];
+                    a_ldmatrix_x4(a0, qa + k);
+                    a_ldmatrix_x4(a1, qa + k + 16);
+                    a_ldmatrix_x4(b, kb + k);
+                    a_mma_bf16(s[0], a0, b[0], b[1]);
+                    a_mma_bf16(s[1], a1, b[2], b[3]);
+                }
+                if (k < DK) {       // a last step of 16 (the row's pad keeps the ldmatrix inside the tile)
+                    unsigned a0[4], b[4];
+                    a_ldmatrix_x4(a0, qa + k);
+                    a_ldmatrix_x4(b, kb + k - 16);
+                    a_mma_bf16(s[0], a0, b[2], b[3]);
+                }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[0][e] += s[1][e];
             }
         }
-        const int jbase = lo + it * AN + wq * 16 + (lane & 3) * 2;
+        const int jbase = lo + it * AN + wq * KW + (lane & 3) * 2;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int jn = 0; jn < 2; ++jn)
+        for (int jn = 0; jn < NJS; ++jn)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int j = jbase + jn * 8 + e;
@@ -500,15 +530,15 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         if ((lane & 3) == 0) {
-            red_max[(rg * 4 + wq) * 16 + (lane >> 2)] = mx0;
-            red_max[(rg * 4 + wq) * 16 + (lane >> 2) + 8] = mx1;
+            red_max[(rg * NQ + wq) * 16 + (lane >> 2)] = mx0;
+            red_max[(rg * NQ + wq) * 16 + (lane >> 2) + 8] = mx1;
         }
         __syncthreads();
         float n0 = m0, n1 = m1;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            n0 = fmaxf(n0, red_max[(rg * 4 + w) * 16 + (lane >> 2)]);
-            n1 = fmaxf(n1, red_max[(rg * 4 + w) * 16 + (lane >> 2) + 8]);
+        for (int w = 0; w < NQ; ++w) {
+            n0 = fmaxf(n0, red_max[(rg * NQ + w) * 16 + (lane >> 2)]);
+            n1 = fmaxf(n1, red_max[(rg * NQ + w) * 16 + (lane >> 2) + 8]);
         }
         const float s0 = n0 == -INFINITY ? 0.f : n0, s1 = n1 == -INFINITY ? 0.f : n1;
         const float alpha0 = expf(m0 - s0), alpha1 = expf(m1 - s1);
@@ -516,12 +546,12 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
         m1 = n1;
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-        for (int jn = 0; jn < 2; ++jn) {
+        for (int jn = 0; jn < NJS; ++jn) {
             const float p00 = expf(s[jn][0] - s0), p01 = expf(s[jn][1] - s0);
             const float p10 = expf(s[jn][2] - s1), p11 = expf(s[jn][3] - s1);
             ps0 += p00 + p01;
             ps1 += p10 + p11;
-            const int col = wq * 16 + jn * 8 + (lane & 3) * 2;
+            const int col = wq * KW + jn * 8 + (lane & 3) * 2;
             *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * PLD + col) = __floats2bfloat162_rn(p00, p01);
             *reinterpret_cast<__nv_bfloat162*>(Ps + r1 * PLD + col) = __floats2bfloat162_rn(p10, p11);
         }
@@ -558,15 +588,15 @@ attn_latent_mma_kernel(const __nv_bfloat16* q_lat, const __nv_bfloat16* q, const
     l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     __syncthreads();
     if ((lane & 3) == 0) {
-        red_sum[(rg * 4 + wq) * 16 + (lane >> 2)] = l0;
-        red_sum[(rg * 4 + wq) * 16 + (lane >> 2) + 8] = l1;
+        red_sum[(rg * NQ + wq) * 16 + (lane >> 2)] = l0;
+        red_sum[(rg * NQ + wq) * 16 + (lane >> 2) + 8] = l1;
     }
     __syncthreads();
     float t0 = 0.f, t1 = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-        t0 += red_sum[(rg * 4 + w) * 16 + (lane >> 2)];
-        t1 += red_sum[(rg * 4 + w) * 16 + (lane >> 2) + 8];
+    for (int w = 0; w < NQ; ++w) {
+        t0 += red_sum[(rg * NQ + w) * 16 + (lane >> 2)];
+        t1 += red_sum[(rg * NQ + w) * 16 + (lane >> 2) + 8];
     }
     if (nsplit > 1) {
         // my share, not normalised, with its maximum and sum: the merge kernel finishes the rows
@@ -619,31 +649,37 @@ TK_API int tk_attn_latent_mma(const void* q_lat, const void* q, const void* cach
                               const int* tok_seq, const int* block_table, int bt_stride, const int* tile_tok0,
                               const int* tile_ntok, int n_tiles, int tokens_per_tile, int tokens, int H, int D, int R,
                               int Dr, int P, int window, float scale, int nsplit, float* part_o, float* part_ml,
-                              cudaStream_t stream) {
+                              int rows16, cudaStream_t stream) {
     TK_CHECK_ARG(nsplit >= 1 && nsplit <= 64 && (nsplit == 1 || (part_o != nullptr && part_ml != nullptr)),
                  "latent attention (mma): %d shares of the keys need scratch memory", nsplit);
     TK_CHECK_ARG(tk_attn_latent_mma_supported(D, R, Dr), "latent attention (mma): sizes D=%d R=%d Dr=%d", D, R, Dr);
     TK_CHECK_ARG(H > 0 && P > 0 && n_tiles >= 0 && tokens >= 0, "latent attention (mma): bad counts");
     TK_CHECK_ARG(tokens_per_tile >= 1 && tokens_per_tile <= AM, "latent attention (mma): %d tokens per tile", tokens_per_tile);
     if (n_tiles == 0) return 0;
-    const int hpc = min(H, AM / tokens_per_tile);
+    // one row group of 16 rows for tiles of one token (steps of single tokens), where the latent
+    // divides over eight warps
+    const bool one = rows16 != 0 && tokens_per_tile == 1 && R % 64 == 0;
+    const int am = one ? 16 : AM;
+    const int hpc = min(H, am / tokens_per_tile);
     const int KLD = R + Dr + 8;
-    const size_t smem = (size_t)(AM + 2 * AN) * KLD * 2 + (size_t)AM * PLD * 2 + 256 * sizeof(float);
+    const size_t smem = (size_t)(am + 2 * AN) * KLD * 2 + (size_t)am * PLD * 2 + 256 * sizeof(float);
     dim3 grid(n_tiles, (H + hpc - 1) / hpc, nsplit);
-#define TK_ALM(NB)                                                                                                 \
+#define TK_ALM2(NB, RGV)                                                                                           \
     do {                                                                                                           \
-        cudaFuncSetAttribute(attn_latent_mma_kernel<NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-        tk_launch(attn_latent_mma_kernel<NB>, grid, dim3(A_THREADS), smem, stream, (const __nv_bfloat16*)q_lat,     \
+        cudaFuncSetAttribute(attn_latent_mma_kernel<NB, RGV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        tk_launch(attn_latent_mma_kernel<NB, RGV>, grid, dim3(A_THREADS), smem, stream, (const __nv_bfloat16*)q_lat, \
                   (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, (__nv_bfloat16*)out, positions, tok_seq,   \
                   block_table, bt_stride, tile_tok0, tile_ntok, tokens, H, D, R, Dr, P, window, scale, hpc, nsplit, \
                   part_o, part_ml);                                                                                \
     } while (0)
-    const int nb = R / 32;
+#define TK_ALM(NB) do { if (one) TK_ALM2(NB, 1); else TK_ALM2(NB, 2); } while (0)
+    const int nb = one ? R / 64 : R / 32;
     if (nb <= 2) TK_ALM(2);
     else if (nb <= 4) TK_ALM(4);
     else if (nb <= 8) TK_ALM(8);
     else TK_ALM(16);
 #undef TK_ALM
+#undef TK_ALM2
     TK_CHECK_LAUNCH("attn_latent_mma");
     return 0;
 }

@@ -943,11 +943,12 @@ ATTENTION_LATENT_MAX_RANK = 512
 def attention_latent(q_lat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor,
                      tok_seq: torch.Tensor, block_table: torch.Tensor, tile_tok0: torch.Tensor,
                      tile_ntok: torch.Tensor, tokens_per_tile: int, heads: int, dim: int, rot_dim: int,
-                     window: int | None, scale: float, nsplit: int = 1) -> torch.Tensor:
+                     window: int | None, scale: float, nsplit: int = 1, rows16: bool = False) -> torch.Tensor:
     """Windowed causal attention over the latent cache [pages, P, R + rot_dim]: scores
     ``(q_lat[h, t] . c_j + q[t, h, dim:] . k_rot_j) * scale``, output ``sum_j p_j c_j`` as [heads, T, R].
     ``nsplit`` > 1 (tensor-core form only): that many CTAs share a tile's keys and a second kernel
-    merges their shares, for steps with few tiles behind long contexts."""
+    merges their shares, for steps with few tiles behind long contexts. ``rows16`` (with one token a
+    tile): the tensor-core form with all of its warps on one group of 16 rows (a token's heads)."""
     _cuda(q_lat, q, cache, positions, tok_seq, block_table, tile_tok0, tile_ntok)
     H, T, R = q_lat.shape
     if (H != heads or not q_lat.is_contiguous() or not q.is_contiguous() or q.shape[0] != T
@@ -960,9 +961,9 @@ def attention_latent(q_lat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, 
                   _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
                   _ptr(_i32(tile_tok0, "tile_tok0")), _ptr(_i32(tile_ntok, "tile_ntok")), tile_tok0.numel(),
                   int(tokens_per_tile), T, H, dim, R, rot_dim, cache.shape[1], int(window or 0), float(scale), 1, None,
-                  None, _stream()) if nsplit <= 1 else _attention_latent_split(
+                  None, int(bool(rows16)), _stream()) if nsplit <= 1 else _attention_latent_split(
                       q_lat, q, cache, out, positions, tok_seq, block_table, tile_tok0, tile_ntok, tokens_per_tile, dim,
-                      rot_dim, window, scale, int(nsplit))
+                      rot_dim, window, scale, int(nsplit), rows16)
         return out
     _lib.call("tk_attn_latent", _ptr(q_lat), _ptr(q), _ptr(cache), _ptr(out), _ptr(_i32(positions, "positions")),
               _ptr(_i32(tok_seq, "tok_seq")), _ptr(_i32(block_table, "block_table")), block_table.stride(0),
@@ -973,14 +974,14 @@ def attention_latent(q_lat: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, 
 
 
 def _attention_latent_split(q_lat, q, cache, out, positions, tok_seq, block_table, tile_tok0, tile_ntok,
-                            tokens_per_tile, dim, rot_dim, window, scale, nsplit) -> None:
+                            tokens_per_tile, dim, rot_dim, window, scale, nsplit, rows16=False) -> None:
     H, T, R = q_lat.shape
     part_o = torch.empty(nsplit, H, T, R, dtype=torch.float32, device=q.device)
     part_ml = torch.empty(nsplit, H, T, 2, dtype=torch.float32, device=q.device)
     _lib.call("tk_attn_latent_mma", _ptr(q_lat), _ptr(q), _ptr(cache), _ptr(out), _ptr(positions), _ptr(tok_seq),
               _ptr(block_table), block_table.stride(0), _ptr(tile_tok0), _ptr(tile_ntok), tile_tok0.numel(),
               int(tokens_per_tile), T, H, dim, R, rot_dim, cache.shape[1], int(window or 0), float(scale), nsplit,
-              _ptr(part_o), _ptr(part_ml), _stream())
+              _ptr(part_o), _ptr(part_ml), int(bool(rows16)), _stream())
     _lib.call("tk_attn_latent_merge", _ptr(part_o), _ptr(part_ml), _ptr(out), H * T, R, nsplit, _stream())
 
 

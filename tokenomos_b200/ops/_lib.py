@@ -78,7 +78,7 @@ _SIGNATURES = {
     "tk_attn_latent": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P],
     "tk_attn_latent_mma_rows": [],
     "tk_attn_latent_mma_supported": [I, I, I],
-    "tk_attn_latent_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P, P],
+    "tk_attn_latent_mma": [P, P, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, I, I, F, I, P, P, I, P],
     "tk_attn_latent_merge": [P, P, P, I, I, I, P],
     "tk_head_gate_transpose": [P, P, L, P, I, I, I, I, P],
     "tk_moe_route": [P, L, I, I, I, F, I, P, P, P, P],

@@ -70,7 +70,7 @@ class LatentAttention:
             return 1
         longest = ctx.host.longest if self.window is None else min(ctx.host.longest, self.window)
         key_tiles = -(-max(1, longest) // 64) + 1
-        chunks = -(-self.heads // min(self.heads, max(1, 32 // per_tile)))
+        chunks = -(-self.heads // min(self.heads, 16 if self.kv_rank % 64 == 0 else 32))
         ctas = max(1, ctx.n_tokens * chunks)
         return max(1, min(-(-key_tiles // 2), 16, (2 * self.tuning.sm_count) // ctas))
 
@@ -86,10 +86,15 @@ class LatentAttention:
         q_nope = q.view(T, H, self.dim + self.rot_dim)[:, :, :self.dim].transpose(0, 1)      # [H, T, dim]
         q_lat = ops.gemm_batched(q_nope, self.uk_t)                                          # [H, T, kv_rank]
         per_tile = ops.attention_latent_tokens(H, self.dim, self.kv_rank, self.rot_dim, q.dtype)
+        # a step of single tokens: every tile is one token's heads, and the tensor-core form puts
+        # all of its warps on 16 rows
+        single = ctx.host.decode_only and ops.attention_latent_mma_supported(self.dim, self.kv_rank, self.rot_dim, q.dtype)
+        if single:
+            per_tile = 1
         _, tok0, _, ntok = ctx.tiles(per_tile)
         lat = ops.attention_latent(q_lat, q, cache, ctx.positions, ctx.tok_seq, table, tok0, ntok, per_tile, H,
                                    self.dim, self.rot_dim, self.window, self.scale,
-                                   nsplit=self.decode_splits(ctx, per_tile, q.dtype))         # [H, T, kv_rank]
+                                   nsplit=self.decode_splits(ctx, per_tile, q.dtype), rows16=single)  # [H, T, kv_rank]
         n = self.q_rank + self.kv_rank + self.rot_dim
         gate = proj[:, n:n + H] if self.gated else None
         if self.fused_gate and lat.dtype == torch.bfloat16:
